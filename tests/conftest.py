@@ -1,0 +1,23 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+REFERENCE_ROOT = os.environ.get("KVB_REFERENCE_ROOT", "/root/reference")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the GPU box)")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    from oracle import kvarn_oracle
+
+    kvarn_oracle.build()
+    return kvarn_oracle
