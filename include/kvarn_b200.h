@@ -1,0 +1,140 @@
+/*
+ * kvarn_b200.h -- C ABI of the B200 (sm_100a) KVarN quantized paged KV-cache library.
+ *
+ * Drop-in boundary for the reference's kvarn-port operator API.  Every entry point names the
+ * reference interface it replaces (paths relative to the reference repository root;
+ * LAUNCH.h = kvarn-port/engine/src/ops/kv_cache/append/kvarn128_launch.h,
+ * LAUNCH.cu = the .cu beside it, P3 = kvarn-port/patches/0003-*.patch).
+ *
+ * Conventions
+ *   - plain pointers and sizes; every buffer is caller-owned DEVICE memory unless stated.
+ *   - `stream` is a cudaStream_t passed as void*.
+ *   - calls are asynchronous on `stream`; none synchronises, none allocates (except the
+ *     one-time set-up noted at kvb_attn_decode_static).
+ *   - no exceptions cross the ABI: functions return a kvb_status; kvb_last_error_string()
+ *     gives the text of the calling thread's last failure.
+ *   - positions and block tables are read on the device only (the reference's hard rule,
+ *     LAUNCH.cu:5-11): the host never dereferences them.
+ *
+ * Memory layout (identical to the reference's P1 planes, kvarn_layout.h:61-131, generalised to
+ * S = head_dim/128 in {1,2} slices):
+ *   k_code, v_code : u8  {head_dim/2, 64, kv_heads, pages}   byte b of a token row = dims 2b | 2b+1<<4
+ *   k_scale        : f16 {5S, 64, kv_heads, pages}           cols [0,2S) scale_axis[dim 2S*row+col],
+ *                                                            [2S,4S) zp_axis, 4S+s other_axis[token row]
+ *   v_scale        : f16 {4S, 64, kv_heads, pages}           cols [0,2S) other_axis[dim], 2S+s scale_axis[token],
+ *                                                            3S+s zp_axis[token]
+ *   element offset = L*64*(head + kv_heads*page) + L*page_off + slot   (kvarn_layout.h:90-97)
+ *   stage          : f16 [K|V][slot = tile%2][kv_heads][128][head_dim] rotated, un-quantised rows of the
+ *                    open tile; persistent state of the layer (LAUNCH.cu:262-273), kvb_stage_bytes().
+ *   tile t (128 tokens) = logical pages 2t, 2t+1 -> physical pages table[2t], table[2t+1].
+ */
+#ifndef KVARN_B200_H
+#define KVARN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum kvb_status {
+    KVB_OK = 0,
+    KVB_EINVAL = 1,   /* bad argument (the reference throws std::invalid_argument, LAUNCH.cu:1024-1061) */
+    KVB_ECUDA = 2,    /* a CUDA call failed (the reference's CUDA_CHECK, LAUNCH.cu:1075-1091) */
+    KVB_ERANGE = 3,   /* a size exceeds what the call supports */
+    KVB_ETIMEOUT = 4  /* a bounded device-side wait gave up (read from the error word) */
+} kvb_status;
+
+enum { KVB_DTYPE_F16 = 0, KVB_DTYPE_BF16 = 1 };
+
+/* One layer's cache, passed by pointer to every call (host struct of device pointers).
+ * Replaces the argument list of kv_cache_append_kvarn128_launch (LAUNCH.h:40-44) and the
+ * KvarnTile128BlockTable descriptor (LAUNCH.h:21-36). */
+typedef struct kvb_layer {
+    uint8_t* k_code;
+    void* k_scale;
+    uint8_t* v_code;
+    void* v_scale;
+    void* stage;                 /* kvb_stage_bytes(head_dim, kv_heads) bytes, zero-initialised by the caller */
+    const int32_t* table_direct; /* resolved table, or NULL to use tables + table_rows[0]*table_stride */
+    const int32_t* tables;
+    const int32_t* table_rows;
+    int32_t table_stride;
+    int32_t table_len;           /* entries readable in the resolved table (bounds check on device) */
+    int32_t pages;               /* physical pages in the planes */
+    int32_t kv_heads;            /* 1..8 */
+    int32_t q_heads;             /* multiple of kv_heads; q_heads/kv_heads <= 8 */
+    int32_t head_dim;            /* 128 or 256 */
+    int32_t dtype;               /* KVB_DTYPE_* of k, v, q and out */
+    int32_t sinkhorn_iters;      /* 0 = bit-exact regime; the reference engine's default is 16 */
+    uint32_t* error_word;        /* optional device word: kernels OR in a code instead of faulting */
+} kvb_layer;
+
+/* bits OR-ed into *error_word */
+enum { KVB_ERR_PAGE_RANGE = 1u, KVB_ERR_TABLE_RANGE = 2u, KVB_ERR_WAIT_TIMEOUT = 4u, KVB_ERR_POSITIONS = 8u };
+
+const char* kvb_last_error_string(void);
+int kvb_version(void);
+
+/* Sizes. */
+size_t kvb_stage_bytes(int head_dim, int kv_heads);
+size_t kvb_plane_bytes(int which /*0 k_code,1 k_scale,2 v_code,3 v_scale*/, int head_dim, int kv_heads, int pages);
+
+/* Append `tokens` contiguous positions positions_dev[0..tokens) of one sequence: rotate the rows into the
+ * stage, and quantise every tile the append completes into its two pages.
+ * k, v: [tokens][kv_heads][head_dim], dim fastest (LAUNCH.cu:111-113).
+ * Replaces kv_cache_append_kvarn128_launch (LAUNCH.h:40-44, LAUNCH.cu:1018-1097). */
+int kvb_append(const kvb_layer* layer, const void* k, const void* v, const int32_t* positions_dev, int tokens,
+               void* stream);
+
+/* De-quantise tile `tile` of head `head` to rotated-domain fp16 [128][head_dim] (out_k, out_v).
+ * Replaces kvarn128_decode_tile (LAUNCH.h:56-58, LAUNCH.cu:1099-1115). */
+int kvb_decode_tile(const kvb_layer* layer, int tile, int head, void* out_k, void* out_v, void* stream);
+
+/* Split count and workspace size for the attention calls.
+ * Replace causal_attention_split_capacity (P3:3326-3380) and the partial_acc/partial_m/partial_l tensors
+ * the reference's callers allocate (P3:3612-3616). rows = query tokens per call (1 decode, 1..8 verify). */
+int kvb_split_capacity(int kv_len_max, int kv_heads, int q_heads, int rows, int batch);
+size_t kvb_workspace_bytes(int kv_len_max, int kv_heads, int q_heads, int head_dim, int rows, int batch);
+
+/* Decode attention of one query token over the cache (the token at *pos_dev is already appended):
+ * out = softmax(scale * q K^T) V over keys 0..pos, keys of sealed tiles read from the quantised pages
+ * (de-quantisation fused into the QK and PV loops), keys of the open tile from the stage.
+ * q, out: [q_heads][head_dim].  kv_len_max: host upper bound of pos+1 (sizes the grid, graph-stable).
+ * workspace: kvb_workspace_bytes(kv_len_max, ..., rows=1, batch=1) bytes.
+ * Replaces causal_attention_cached_small_t_launch (P3:3612-3696). */
+int kvb_attn_decode(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
+                    void* workspace, void* out, void* stream);
+
+/* Same, but stops before the final normalisation: writes the log-sum-exp partial of keys
+ * [key_begin, key_end) -- part_m[q_heads] (max logit, natural log units), part_l[q_heads] (sum of
+ * exp(logit - m)), part_o[q_heads][head_dim] (sum of exp(logit - m) * V, rotated domain), fp32.
+ * One GPU's contribution to a sequence-range sharded decode. No counterpart in the reference (single GPU). */
+int kvb_attn_decode_partial(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale,
+                            int kv_len_max, int key_begin, int key_end, void* workspace, float* part_m,
+                            float* part_l, float* part_o, void* stream);
+
+/* Merge `parts` partial sets laid out [parts][q_heads](m), [parts][q_heads](l), [parts][q_heads][head_dim](o):
+ * log-sum-exp merge, normalise, inverse rotation, write out [q_heads][head_dim] in `dtype`.
+ * Replaces causal_attention_small_t_reduce_output_kernel (P3:3467-3482) for the cross-GPU step. */
+int kvb_merge_partials(const float* parts_m, const float* parts_l, const float* parts_o, int parts, int q_heads,
+                       int head_dim, int dtype, void* out, void* stream);
+
+/* MTP verify: append `width` (1..8) new rows, then causal attention of those rows (row i sees keys
+ * 0..positions[i]).  q, out: [width][q_heads][head_dim]; k, v: [width][kv_heads][head_dim].
+ * Replaces causal_attention_small_t_launch (P3:3508-3610). */
+int kvb_attn_verify(const kvb_layer* layer, const void* q, const void* k, const void* v, const int32_t* positions_dev,
+                    int width, float scale, int kv_len_max, void* workspace, void* out, void* stream);
+
+/* Prefill chunk: quantise-append `tokens` rows, then causal attention of the chunk over prefix + chunk.
+ * q, out: [tokens][q_heads][head_dim].  Replaces causal_attention_prompt_launch (P3:2362-2416). */
+int kvb_attn_prefill(const kvb_layer* layer, const void* q, const void* k, const void* v,
+                     const int32_t* positions_dev, int tokens, float scale, int kv_len_max, void* workspace,
+                     void* out, void* stream);
+size_t kvb_prefill_workspace_bytes(int kv_len_max, int kv_heads, int q_heads, int head_dim, int tokens);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVARN_B200_H */

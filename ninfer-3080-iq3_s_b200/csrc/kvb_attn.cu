@@ -1,0 +1,739 @@
+// kvb_attn.cu -- paged split-K attention over the quantised cache for 1..8 query tokens (decode, MTP
+// verify), de-quantisation fused into the QK and PV loops.  head_dim 128.
+//
+// Grid (splits + 1, kv heads, row blocks).  A CTA owns one KV head, one contiguous range of sealed pages
+// and a block of up to 16 GQA-merged query rows (row = token * G + q head within the KV head); the extra
+// CTA in x handles the open tile, whose rows are still un-quantised fp16 in the stage.  Inside a CTA each
+// of the 8 warps streams its own sub-range of pages through a private two-slot shared-memory ring filled
+// by bulk async copies (one mbarrier per slot, four contiguous runs per page: K codes, V codes, K scales,
+// V scales), so warps never synchronise with each other until the final merge.
+//
+// Math per page (quantised-domain identities, no per-element de-quantisation):
+//   logit[r][j] = other_K[j] * ( sum_d (q'[r][d] * scale_K[d]) * code_K[j][d]  +  sum_d q'[r][d] * zp_K[d] )
+//   o[r][d]    += other_V[d] * ( sum_j (p[r][j] * scale_V[j]) * code_V[j][d]  +  sum_j p[r][j] * zp_V[j] )
+// with q' = H q * softmax_scale * log2(e).  The two contractions run on the warp-level tensor cores
+// (m16n8k16, fp16 operands, fp32 accumulate): 4-bit codes are exact in fp16, q' * scale_K is split into
+// an fp16 high and low part so the product keeps fp32 accuracy, and p * scale_V is rounded to fp16 once.
+// Codes are unpacked with one logic op per pair (see unpack8); V pairs are formed across two tokens with
+// a byte permute so that no transpose through shared memory is needed.
+#include <climits>
+
+#include "kvb_common.cuh"
+#include "kvb_ptx.cuh"
+
+namespace kvb {
+namespace {
+
+constexpr int D = 128;
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kRows = 16;  // query rows per CTA (one MMA M block)
+constexpr int kKCodeOff = 0, kVCodeOff = 4096, kKScaleOff = 8192, kVScaleOff = 8832, kPageBytes = 9344;
+constexpr int kSlots = 2;
+constexpr int kScratchBytes = 256 + 256 + 128;  // per warp: scale_K[128], zp_K[128], other_K[64] as fp16
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct AttnParams {
+    LayerView L;
+    const uint16_t* q;   // [T][q_heads][D]
+    const int32_t* pos;  // [T] absolute positions of the query tokens (device)
+    const int32_t* total_pos;  // position of the newest token in the cache (kv_total = *total_pos + 1)
+    int T;
+    float scale_log2;    // softmax scale * log2(e)
+    int nsplit;          // CTAs over sealed pages; blockIdx.x == nsplit is the open-tile CTA
+    int key_begin, key_end;
+    float* ws_m;         // [H][Z][nsplit+1][16]
+    float* ws_l;
+    float* ws_o;         // [H][Z][nsplit+1][16][D]
+};
+
+struct __align__(16) AttnSmem {
+    uint8_t slots[kWarps][kSlots][kPageBytes];
+    uint8_t scratch[kWarps][kScratchBytes];
+    float4 qfrag[2][8][32];  // q' in per-lane fragment order: [row half][j][lane] = dims 32t+4j..+3 of row g(+8)
+    uint64_t bars[kWarps][kSlots];
+    int row_pos[kRows];
+};
+
+// Per-thread state of the running softmax for rows g (index 0) and g + 8 (index 1).
+struct Acc {
+    float o[16][4];  // PV accumulators: n-block nb holds dims 32t+nb (c0/c2) and 32t+16+nb (c1/c3)
+    float m[2], l[2], z[2];
+};
+
+struct QFrag {
+    uint32_t hi[8][4];  // A fragments of q' * scale_K, per k-block: a0 a1 a2 a3
+    uint32_t lo[8][4];
+    float qz[2];        // sum_d q'[row][d] * zp_K[d]
+};
+
+// Build the A fragments for one tile from q' (shared memory, fragment order) and the tile's per-dim
+// scale / zero point (warp scratch, natural dim order).  k-slot pairing follows unpack8:
+// word i of the lane's 32-dim chunk feeds k-blocks 2i (dims +0,+4 | +1,+5) and 2i+1 (dims +2,+6 | +3,+7).
+template <bool kScaled>
+__device__ __forceinline__ void build_qfrag(const AttnSmem& sm, const uint8_t* scratch, int lane, QFrag& f) {
+    const int t = lane & 3;
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+        float qs[32];
+        float qz = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float4 qv = sm.qfrag[hf][j][lane];
+            if constexpr (kScaled) {
+                const uint2 ks = *reinterpret_cast<const uint2*>(scratch + (32 * t + 4 * j) * 2);
+                const uint2 kz = *reinterpret_cast<const uint2*>(scratch + 256 + (32 * t + 4 * j) * 2);
+                const float2 s01 = unpack_half2(ks.x), s23 = unpack_half2(ks.y);
+                const float2 z01 = unpack_half2(kz.x), z23 = unpack_half2(kz.y);
+                qs[4 * j + 0] = qv.x * s01.x; qs[4 * j + 1] = qv.y * s01.y;
+                qs[4 * j + 2] = qv.z * s23.x; qs[4 * j + 3] = qv.w * s23.y;
+                qz = fmaf(qv.x, z01.x, qz); qz = fmaf(qv.y, z01.y, qz);
+                qz = fmaf(qv.z, z23.x, qz); qz = fmaf(qv.w, z23.y, qz);
+            } else {
+                qs[4 * j + 0] = qv.x; qs[4 * j + 1] = qv.y; qs[4 * j + 2] = qv.z; qs[4 * j + 3] = qv.w;
+            }
+        }
+        qz += __shfl_xor_sync(0xffffffffu, qz, 1);
+        qz += __shfl_xor_sync(0xffffffffu, qz, 2);
+        f.qz[hf] = qz;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                // quantised pages: pairs (e, e+4) of word i.  stage rows (un-quantised): natural pairs (2e, 2e+1).
+                const float x0 = kScaled ? qs[8 * i + e] : qs[8 * i + 2 * e];
+                const float x1 = kScaled ? qs[8 * i + e + 4] : qs[8 * i + 2 * e + 1];
+                const uint32_t h = pack_half2(x0, x1);
+                const float2 hf32 = unpack_half2(h);
+                const uint32_t l = pack_half2(x0 - hf32.x, x1 - hf32.y);
+                // e = 0,1 -> k-block 2i (a0 | a2); e = 2,3 -> k-block 2i+1
+                const int kb = 2 * i + (e >> 1), reg = (e & 1) * 2 + hf;
+                f.hi[kb][reg] = h;
+                f.lo[kb][reg] = l;
+            }
+        }
+    }
+}
+
+// Scale page of K -> warp scratch in natural dim order.  A page row is 5 halves
+// [scale(2r) scale(2r+1) zp(2r) zp(2r+1) other(r)]; lane l re-packs rows 2l and 2l+1 (20 bytes).
+__device__ __forceinline__ void transpose_k_scale(const uint8_t* kscale_page, uint8_t* scratch, int lane) {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(kscale_page + 20 * lane);
+    const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3], w4 = w[4];
+    // halves: w0 = s(4l) s(4l+1) | w1 = z(4l) z(4l+1) | w2 = o(2l) s(4l+2) | w3 = s(4l+3) z(4l+2) | w4 = z(4l+3) o(2l+1)
+    *reinterpret_cast<uint2*>(scratch + 8 * lane) = make_uint2(w0, prmt(w2, w3, 0x5432));
+    *reinterpret_cast<uint2*>(scratch + 256 + 8 * lane) = make_uint2(w1, prmt(w3, w4, 0x5432));
+    *reinterpret_cast<uint32_t*>(scratch + 512 + 4 * lane) = prmt(w2, w4, 0x7610);
+}
+
+// Online-softmax update of one 64-key block whose logits (log2 units) sit in s[8][4]
+// (n-block nbk = 2*grp + nb: c0,c1 = row g, keys 16grp + 8nb + 2t, +1; c2,c3 = row g+8).
+// On return s holds p = exp2(logit - m_new); acc is rescaled if a row maximum moved.
+template <bool kUpper>
+__device__ __forceinline__ void softmax_block(float (&s)[8][4], Acc& acc) {
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
+        if constexpr (kUpper) mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
+    }
+#pragma unroll
+    for (int hf = 0; hf < (kUpper ? 2 : 1); ++hf) {
+        mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
+        mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
+    }
+    float mnew[2], muse[2], alpha[2];
+    bool moved = false;
+#pragma unroll
+    for (int hf = 0; hf < (kUpper ? 2 : 1); ++hf) {
+        mnew[hf] = fmaxf(acc.m[hf], mx[hf]);
+        moved |= mnew[hf] > acc.m[hf];
+        muse[hf] = mnew[hf] == -INFINITY ? 0.0f : mnew[hf];
+        alpha[hf] = fast_exp2(acc.m[hf] - muse[hf]);
+        acc.m[hf] = mnew[hf];
+    }
+    if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+            acc.o[n][0] *= alpha[0]; acc.o[n][1] *= alpha[0];
+            if constexpr (kUpper) { acc.o[n][2] *= alpha[1]; acc.o[n][3] *= alpha[1]; }
+        }
+        acc.l[0] *= alpha[0]; acc.z[0] *= alpha[0];
+        if constexpr (kUpper) { acc.l[1] *= alpha[1]; acc.z[1] *= alpha[1]; }
+    }
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        s[n][0] = fast_exp2(s[n][0] - muse[0]); s[n][1] = fast_exp2(s[n][1] - muse[0]);
+        acc.l[0] += s[n][0] + s[n][1];
+        if constexpr (kUpper) {
+            s[n][2] = fast_exp2(s[n][2] - muse[1]); s[n][3] = fast_exp2(s[n][3] - muse[1]);
+            acc.l[1] += s[n][2] + s[n][3];
+        } else {
+            s[n][2] = 0.0f; s[n][3] = 0.0f;
+        }
+    }
+}
+
+// Key-position mask of a 64-key block starting at absolute position `first`.
+__device__ __forceinline__ void mask_block(float (&s)[8][4], int first, int lane, const int (&row_lim)[2], int key_begin,
+                                           int key_end) {
+    const int t = lane & 3;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        const int p0 = first + (n >> 1) * 16 + (n & 1) * 8 + 2 * t;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int p = p0 + (e & 1);
+            if (p > row_lim[e >> 1] || p < key_begin || p >= key_end) s[n][e] = -INFINITY;
+        }
+    }
+}
+
+// One sealed page (64 keys) of one KV head, staged in shared memory at `pg`.
+template <bool kUpper, bool kOther>
+__device__ __forceinline__ void process_page(const uint8_t* pg, const uint8_t* scratch, const QFrag& qf, Acc& acc, int lane,
+                                             bool need_mask, int first_pos, const int (&row_lim)[2], int key_begin,
+                                             int key_end) {
+    const int g = lane >> 2, t = lane & 3;
+    float s[8][4];
+    // ---- QK: codes of 16 keys x 128 dims per group, two n-blocks of 8 keys
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        const int key = (n >> 1) * 16 + (n & 1) * 8 + g;
+        const uint4 kw = *reinterpret_cast<const uint4*>(pg + kKCodeOff + key * 64 + 16 * t);
+        const uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
+        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t u[4];
+            unpack8(w[i], u);
+            mma16816(c, qf.hi[2 * i][0], qf.hi[2 * i][1], qf.hi[2 * i][2], qf.hi[2 * i][3], u[0], u[1]);
+            mma16816(c, qf.hi[2 * i + 1][0], qf.hi[2 * i + 1][1], qf.hi[2 * i + 1][2], qf.hi[2 * i + 1][3], u[2], u[3]);
+            mma16816(c, qf.lo[2 * i][0], qf.lo[2 * i][1], qf.lo[2 * i][2], qf.lo[2 * i][3], u[0], u[1]);
+            mma16816(c, qf.lo[2 * i + 1][0], qf.lo[2 * i + 1][1], qf.lo[2 * i + 1][2], qf.lo[2 * i + 1][3], u[2], u[3]);
+        }
+        // keys of c0,c1 / c2,c3: 16grp + 8nb + 2t, +1
+        float o0 = 1.0f, o1 = 1.0f;
+        if constexpr (kOther) {
+            const float2 ko = unpack_half2(
+                *reinterpret_cast<const uint32_t*>(scratch + 512 + ((n >> 1) * 16 + (n & 1) * 8 + 2 * t) * 2));
+            o0 = ko.x; o1 = ko.y;
+        }
+        s[n][0] = (c[0] + qf.qz[0]) * o0; s[n][1] = (c[1] + qf.qz[0]) * o1;
+        s[n][2] = (c[2] + qf.qz[1]) * o0; s[n][3] = (c[3] + qf.qz[1]) * o1;
+    }
+    if (need_mask) mask_block(s, first_pos, lane, row_lim, key_begin, key_end);
+    softmax_block<kUpper>(s, acc);
+    // ---- PV: V scale page rows are [other(2r) other(2r+1) scale(r) zp(r)] (8 bytes per key)
+#pragma unroll
+    for (int grp = 0; grp < 4; ++grp) {
+        uint32_t a[4];
+        {
+            const uint4 r0 = *reinterpret_cast<const uint4*>(pg + kVScaleOff + (grp * 16 + 2 * t) * 8);      // keys 2t, 2t+1
+            const uint4 r1 = *reinterpret_cast<const uint4*>(pg + kVScaleOff + (grp * 16 + 8 + 2 * t) * 8);  // keys 2t+8, +9
+            const float2 sz00 = unpack_half2(r0.y), sz01 = unpack_half2(r0.w);
+            const float2 sz10 = unpack_half2(r1.y), sz11 = unpack_half2(r1.w);
+            float(&p0)[4] = s[2 * grp], (&p1)[4] = s[2 * grp + 1];
+            acc.z[0] += p0[0] * sz00.y + p0[1] * sz01.y + p1[0] * sz10.y + p1[1] * sz11.y;
+            a[0] = pack_half2(p0[0] * sz00.x, p0[1] * sz01.x);
+            a[2] = pack_half2(p1[0] * sz10.x, p1[1] * sz11.x);
+            if constexpr (kUpper) {
+                acc.z[1] += p0[2] * sz00.y + p0[3] * sz01.y + p1[2] * sz10.y + p1[3] * sz11.y;
+                a[1] = pack_half2(p0[2] * sz00.x, p0[3] * sz01.x);
+                a[3] = pack_half2(p1[2] * sz10.x, p1[3] * sz11.x);
+            } else {
+                a[1] = 0u; a[3] = 0u;
+            }
+        }
+        // lane (g, t): 16 dims 16g.. of keys 2t, 2t+1 (b0) and 2t+8, 2t+9 (b1)
+        const uint8_t* vb = pg + kVCodeOff + (grp * 16 + 2 * t) * 64 + 8 * g;
+        const uint2 vA = *reinterpret_cast<const uint2*>(vb), vB = *reinterpret_cast<const uint2*>(vb + 64);
+        const uint2 vC = *reinterpret_cast<const uint2*>(vb + 512), vD = *reinterpret_cast<const uint2*>(vb + 576);
+        const uint32_t wa[2] = {vA.x, vA.y}, wb[2] = {vB.x, vB.y}, wc[2] = {vC.x, vC.y}, wd[2] = {vD.x, vD.y};
+#pragma unroll
+        for (int wi = 0; wi < 2; ++wi) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                // four dims 8wi + 4hh + {0..3} of both key pairs: low 16 bits = first key, high 16 bits = second
+                const uint32_t sel = hh ? 0x7632u : 0x5410u;
+                const uint32_t x0 = prmt(wa[wi], wb[wi], sel), x1 = prmt(wc[wi], wd[wi], sel);
+                const uint32_t y0 = x0 >> 8, y1 = x1 >> 8;
+                uint32_t b0[4], b1[4];
+                b0[0] = hsub2_u32(lop3_and_or(x0, 0x000F000Fu, 0x64006400u), 0x64006400u);
+                b0[1] = hsub2_u32(lop3_and_or(x0, 0x00F000F0u, 0x54005400u), 0x54005400u);
+                b0[2] = hsub2_u32(lop3_and_or(y0, 0x000F000Fu, 0x64006400u), 0x64006400u);
+                b0[3] = hsub2_u32(lop3_and_or(y0, 0x00F000F0u, 0x54005400u), 0x54005400u);
+                b1[0] = hsub2_u32(lop3_and_or(x1, 0x000F000Fu, 0x64006400u), 0x64006400u);
+                b1[1] = hsub2_u32(lop3_and_or(x1, 0x00F000F0u, 0x54005400u), 0x54005400u);
+                b1[2] = hsub2_u32(lop3_and_or(y1, 0x000F000Fu, 0x64006400u), 0x64006400u);
+                b1[3] = hsub2_u32(lop3_and_or(y1, 0x00F000F0u, 0x54005400u), 0x54005400u);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mma16816(acc.o[8 * wi + 4 * hh + e], a[0], a[1], a[2], a[3], b0[e], b1[e]);
+            }
+        }
+    }
+}
+
+// 16 keys of the open tile, read un-quantised (fp16, rotated) straight from the stage.
+// krow/vrow point at the first of the 16 stage rows of this head (row stride D halves).
+template <bool kUpper>
+__device__ __forceinline__ void process_stage_group(const __half* krow, const __half* vrow, const QFrag& qf, Acc& acc,
+                                                    int lane, int first_pos, int kv_total, const int (&row_lim)[2],
+                                                    int key_begin, int key_end) {
+    const int g = lane >> 2, t = lane & 3;
+    float s[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = -INFINITY;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+        const __half* kr = krow + (nb * 8 + g) * D + 32 * t;
+        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 kw = *reinterpret_cast<const uint4*>(kr + 8 * i);
+            mma16816(c, qf.hi[2 * i][0], qf.hi[2 * i][1], qf.hi[2 * i][2], qf.hi[2 * i][3], kw.x, kw.y);
+            mma16816(c, qf.hi[2 * i + 1][0], qf.hi[2 * i + 1][1], qf.hi[2 * i + 1][2], qf.hi[2 * i + 1][3], kw.z, kw.w);
+            mma16816(c, qf.lo[2 * i][0], qf.lo[2 * i][1], qf.lo[2 * i][2], qf.lo[2 * i][3], kw.x, kw.y);
+            mma16816(c, qf.lo[2 * i + 1][0], qf.lo[2 * i + 1][1], qf.lo[2 * i + 1][2], qf.lo[2 * i + 1][3], kw.z, kw.w);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int p = first_pos + nb * 8 + 2 * t + (e & 1);
+            s[nb][e] = (p > row_lim[e >> 1] || p >= kv_total || p < key_begin || p >= key_end) ? -INFINITY : c[e];
+        }
+    }
+    softmax_block<kUpper>(s, acc);
+    uint32_t a[4];
+    a[0] = pack_half2(s[0][0], s[0][1]);
+    a[2] = pack_half2(s[1][0], s[1][1]);
+    a[1] = kUpper ? pack_half2(s[0][2], s[0][3]) : 0u;
+    a[3] = kUpper ? pack_half2(s[1][2], s[1][3]) : 0u;
+    // keys at or beyond kv_total hold stale rows: their p is exactly 0; zero V there so 0 * inf cannot appear
+    const __half* vb = vrow + (2 * t) * D + 16 * g;
+    uint4 v[4][2];
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+        const int key = 2 * t + (kk & 1) + (kk >> 1) * 8;
+        const bool live = first_pos + key < kv_total;
+        const uint4* src = reinterpret_cast<const uint4*>(vb + ((kk & 1) + (kk >> 1) * 8) * D);
+        v[kk][0] = live ? src[0] : make_uint4(0, 0, 0, 0);
+        v[kk][1] = live ? src[1] : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int h8 = 0; h8 < 2; ++h8) {
+        const uint32_t wa[4] = {v[0][h8].x, v[0][h8].y, v[0][h8].z, v[0][h8].w};
+        const uint32_t wb[4] = {v[1][h8].x, v[1][h8].y, v[1][h8].z, v[1][h8].w};
+        const uint32_t wc[4] = {v[2][h8].x, v[2][h8].y, v[2][h8].z, v[2][h8].w};
+        const uint32_t wd[4] = {v[3][h8].x, v[3][h8].y, v[3][h8].z, v[3][h8].w};
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            // register r holds dims 8 h8 + 2r, +1 of one key; pair them across keys (2t, 2t+1) and (2t+8, 2t+9)
+            mma16816(acc.o[8 * h8 + 2 * r], a[0], a[1], a[2], a[3], prmt(wa[r], wb[r], 0x5410), prmt(wc[r], wd[r], 0x5410));
+            mma16816(acc.o[8 * h8 + 2 * r + 1], a[0], a[1], a[2], a[3], prmt(wa[r], wb[r], 0x7632), prmt(wc[r], wd[r], 0x7632));
+        }
+    }
+}
+
+template <bool kUpper, bool kOther>
+__global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    AttnSmem& sm = *reinterpret_cast<AttnSmem*>(smem_raw);
+    const LayerView& L = P.L;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y, zb = blockIdx.z, split = blockIdx.x;
+    const int G = L.q_heads / L.kv_heads;
+    const int kv_total = *P.total_pos + 1;
+    const int key_end = min(P.key_end, kv_total), key_begin = max(P.key_begin, 0);
+    const int sealed_pages = 2 * (kv_total / kTile);
+
+    // ---- q' = H q * scale * log2(e) for the 16 rows of this block, stored in fragment order
+    for (int r = warp; r < kRows; r += kWarps) {
+        const int R = zb * kRows + r, tq = R / G, gq = R % G;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        int rp = -1;
+        if (tq < P.T) {
+            const uint16_t* qrow = P.q + (static_cast<int64_t>(tq) * L.q_heads + head * G + gq) * D;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                v[j] = L.dtype == KVB_DTYPE_BF16 ? in_to_f32<true>(qrow[lane + 32 * j]) : in_to_f32<false>(qrow[lane + 32 * j]);
+            hadamard_warp<D>(v, lane);
+            rp = P.pos[tq];
+        }
+        if (lane == 0) sm.row_pos[r] = rp;
+        float* dst = reinterpret_cast<float*>(sm.qfrag);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int d = lane + 32 * j;  // -> lane' = (r%8)*4 + d/32, slot j' = (d%32)/4, component d%4
+            dst[(((r >> 3) * 8 + ((d & 31) >> 2)) * 32 + (r & 7) * 4 + (d >> 5)) * 4 + (d & 3)] = v[j] * P.scale_log2;
+        }
+    }
+    uint64_t* bars = sm.bars[warp];
+    if (lane == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const int g = lane >> 2;
+    int row_lim[2] = {sm.row_pos[g], sm.row_pos[g + 8]};
+    int min_lim = INT_MAX;
+    for (int r = 0; r < kRows; ++r)
+        if (sm.row_pos[r] >= 0) min_lim = min(min_lim, sm.row_pos[r]);
+
+    Acc acc;
+#pragma unroll
+    for (int n = 0; n < 16; ++n) acc.o[n][0] = acc.o[n][1] = acc.o[n][2] = acc.o[n][3] = 0.0f;
+    acc.m[0] = acc.m[1] = -INFINITY;
+    acc.l[0] = acc.l[1] = acc.z[0] = acc.z[1] = 0.0f;
+    QFrag qf;
+    bool timed_out = false;
+
+    if (split < P.nsplit) {
+        // ---- sealed pages of this CTA, then of this warp
+        const int pb = min(key_begin / kPage, sealed_pages), pe = min((key_end + kPage - 1) / kPage, sealed_pages);
+        const int n = max(pe - pb, 0);
+        const int c0 = pb + static_cast<int>(static_cast<int64_t>(n) * split / P.nsplit);
+        const int c1 = pb + static_cast<int>(static_cast<int64_t>(n) * (split + 1) / P.nsplit);
+        const int w0 = c0 + (c1 - c0) * warp / kWarps, w1 = c0 + (c1 - c0) * (warp + 1) / kWarps;
+        const int32_t* tbl = L.table();
+        uint8_t* scratch = sm.scratch[warp];
+        auto issue = [&](int lp, int slot) -> bool {  // lane 0: four bulk copies of one page into a slot
+            const int32_t page = L.page_of(tbl, lp);
+            if (page < 0) return false;
+            uint8_t* dst = sm.slots[warp][slot];
+            mbar_expect_tx(&bars[slot], kPageBytes);
+            bulk_g2s(dst + kKCodeOff, L.k_code + page_head_offset(64, L.kv_heads, page, head), 4096, &bars[slot]);
+            bulk_g2s(dst + kVCodeOff, L.v_code + page_head_offset(64, L.kv_heads, page, head), 4096, &bars[slot]);
+            bulk_g2s(dst + kKScaleOff, L.k_scale + page_head_offset(5, L.kv_heads, page, head), 640, &bars[slot]);
+            bulk_g2s(dst + kVScaleOff, L.v_scale + page_head_offset(4, L.kv_heads, page, head), 512, &bars[slot]);
+            return true;
+        };
+        uint32_t ok_mask = 0;  // bit s: slot s holds a page in flight / ready (lane 0 decides, broadcast below)
+        if (lane == 0) {
+            if (w0 < w1 && issue(w0, 0)) ok_mask |= 1u;
+            if (w0 + 1 < w1 && issue(w0 + 1, 1)) ok_mask |= 2u;
+        }
+        ok_mask = __shfl_sync(0xffffffffu, ok_mask, 0);
+        uint32_t phase[2] = {0, 0};
+        int cur_tile = -1;
+        for (int lp = w0; lp < w1; ++lp) {
+            const int slot = (lp - w0) & 1;
+            const bool valid = (ok_mask >> slot) & 1u;
+            if (valid) {
+                if (!mbar_wait_bounded(&bars[slot], phase[slot])) { timed_out = true; break; }
+                phase[slot] ^= 1u;
+                const uint8_t* pg = sm.slots[warp][slot];
+                if ((lp >> 1) != cur_tile) {  // per-dim scale / zero point are per tile (stored in both pages)
+                    cur_tile = lp >> 1;
+                    __syncwarp();
+                    transpose_k_scale(pg + kKScaleOff, scratch, lane);
+                    __syncwarp();
+                    build_qfrag<true>(sm, scratch, lane, qf);
+                } else if constexpr (kOther) {
+                    __syncwarp();
+                    transpose_k_scale(pg + kKScaleOff, scratch, lane);
+                    __syncwarp();
+                }
+                const int first = lp * kPage;
+                const bool need_mask = first + kPage - 1 > min_lim || first < key_begin || first + kPage > key_end;
+                process_page<kUpper, kOther>(pg, scratch, qf, acc, lane, need_mask, first, row_lim, key_begin, key_end);
+            }
+            // refill this slot with the page after next; the generic-proxy reads above must be ordered first
+            __syncwarp();
+            uint32_t nv = 0;
+            if (lane == 0 && lp + 2 < w1) {
+                fence_proxy_async();
+                nv = issue(lp + 2, slot) ? 1u : 0u;
+            }
+            nv = __shfl_sync(0xffffffffu, nv, 0);
+            ok_mask = (ok_mask & ~(1u << slot)) | (nv << slot);
+        }
+        if (timed_out) {
+            if (lane == 0) L.flag(KVB_ERR_WAIT_TIMEOUT);
+            // copies already issued must land before the CTA's shared memory is released: bounded second wait
+            for (int s2 = 0; s2 < kSlots; ++s2)
+                if ((ok_mask >> s2) & 1u) mbar_wait_bounded(&bars[s2], phase[s2]);
+        }
+    } else {
+        // ---- open tile: warp w takes keys 16w .. 16w+15 of the tile, un-quantised, from the stage
+        const int tile = kv_total / kTile, base = tile * kTile;
+        const int first = base + 16 * warp;
+        if (first < key_end && first + 16 > key_begin && first < kv_total) {
+            build_qfrag<false>(sm, nullptr, lane, qf);
+            process_stage_group<kUpper>(L.stage_row(0, tile & 1, head, 16 * warp), L.stage_row(1, tile & 1, head, 16 * warp), qf,
+                                        acc, lane, first, kv_total, row_lim, key_begin, key_end);
+        }
+    }
+
+    // ---- merge the 8 warps of the CTA (log-sum-exp) and store one partial per row
+    __syncthreads();  // every slot has been consumed: the ring memory becomes the merge buffer
+    constexpr int kORow = 4 * 33, kWarpFloats = 3 * kRows + kRows * kORow;
+    float* mb = reinterpret_cast<float*>(sm.slots) + warp * kWarpFloats;
+    const int t = lane & 3;
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+        acc.l[hf] += __shfl_xor_sync(0xffffffffu, acc.l[hf], 1);
+        acc.l[hf] += __shfl_xor_sync(0xffffffffu, acc.l[hf], 2);
+        acc.z[hf] += __shfl_xor_sync(0xffffffffu, acc.z[hf], 1);
+        acc.z[hf] += __shfl_xor_sync(0xffffffffu, acc.z[hf], 2);
+        if (t == 0) {
+            mb[g + 8 * hf] = acc.m[hf];
+            mb[kRows + g + 8 * hf] = acc.l[hf];
+            mb[2 * kRows + g + 8 * hf] = acc.z[hf];
+        }
+    }
+    float* ob = mb + 3 * kRows;
+#pragma unroll
+    for (int nb = 0; nb < 16; ++nb) {
+        ob[g * kORow + t * 33 + nb] = acc.o[nb][0];
+        ob[g * kORow + t * 33 + 16 + nb] = acc.o[nb][1];
+        ob[(g + 8) * kORow + t * 33 + nb] = acc.o[nb][2];
+        ob[(g + 8) * kORow + t * 33 + 16 + nb] = acc.o[nb][3];
+    }
+    __syncthreads();
+    const float* all = reinterpret_cast<const float*>(sm.slots);
+    const int64_t pidx = ((static_cast<int64_t>(head) * gridDim.z + zb) * (P.nsplit + 1) + split) * kRows;
+    for (int e = threadIdx.x; e < kRows * D; e += kThreads) {
+        const int row = e / D, d = e % D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) m = fmaxf(m, all[w * kWarpFloats + row]);
+        float o = 0.0f, l = 0.0f;
+        if (m != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float* wb = all + w * kWarpFloats;
+                const float wt = fast_exp2(wb[row] - m);  // exp2(-inf) = 0 for a warp that saw no key
+                l += wt * wb[kRows + row];
+                o += wt * (wb[3 * kRows + row * kORow + (d >> 5) * 33 + (d & 31)] + wb[2 * kRows + row]);
+            }
+        }
+        P.ws_o[(pidx + row) * D + d] = o;
+        if (d == 0) { P.ws_m[pidx + row] = m; P.ws_l[pidx + row] = l; }
+    }
+}
+
+// Merge the partials of all splits of one query row, normalise, rotate back (H is its own inverse) and
+// store in the output dtype -- or, for a sharded decode, export the merged partial (m in natural-log
+// units, l, o in the rotated domain).  One warp per (token, q head).
+__global__ void __launch_bounds__(128) reduce_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
+                                                     const float* __restrict__ ws_o, int parts, int T, int q_heads,
+                                                     int kv_heads, int zblocks, int dtype, uint16_t* __restrict__ out,
+                                                     float* __restrict__ part_m, float* __restrict__ part_l,
+                                                     float* __restrict__ part_o) {
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= T * q_heads) return;
+    const int G = q_heads / kv_heads, tq = row / q_heads, qh = row % q_heads, head = qh / G, gq = qh % G;
+    const int R = tq * G + gq, zb = R / kRows, r = R % kRows;
+    const int64_t base = (static_cast<int64_t>(head) * zblocks + zb) * parts * kRows + r;
+    float m = -INFINITY;
+    for (int p = 0; p < parts; ++p) m = fmaxf(m, ws_m[base + static_cast<int64_t>(p) * kRows]);
+    float l = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (m != -INFINITY) {
+        for (int p = 0; p < parts; ++p) {
+            const int64_t i = base + static_cast<int64_t>(p) * kRows;
+            const float w = fast_exp2(ws_m[i] - m);
+            l += w * ws_l[i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[j] += w * ws_o[i * D + lane + 32 * j];
+        }
+    }
+    if (part_m != nullptr) {
+        if (lane == 0) { part_m[row] = m * kLn2; part_l[row] = l; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) part_o[static_cast<int64_t>(row) * D + lane + 32 * j] = o[j];
+        return;
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] *= inv;
+    hadamard_warp<D>(o, lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        out[static_cast<int64_t>(row) * D + lane + 32 * j] = dtype == KVB_DTYPE_BF16 ? f32_to_out<true>(o[j]) : f32_to_out<false>(o[j]);
+}
+
+// Cross-GPU (or cross-range) merge of exported partials: parts_m in natural-log units.
+__global__ void __launch_bounds__(128) merge_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
+                                                    const float* __restrict__ po, int parts, int rows, int dtype,
+                                                    uint16_t* __restrict__ out) {
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    float m = -INFINITY;
+    for (int p = 0; p < parts; ++p) m = fmaxf(m, pm[static_cast<int64_t>(p) * rows + row]);
+    float l = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (m != -INFINITY) {
+        for (int p = 0; p < parts; ++p) {
+            const int64_t i = static_cast<int64_t>(p) * rows + row;
+            const float w = __expf(pm[i] - m);
+            l += w * pl[i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[j] += w * po[i * D + lane + 32 * j];
+        }
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] *= inv;
+    hadamard_warp<D>(o, lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        out[static_cast<int64_t>(row) * D + lane + 32 * j] = dtype == KVB_DTYPE_BF16 ? f32_to_out<true>(o[j]) : f32_to_out<false>(o[j]);
+}
+
+int g_sm_count = 0;
+int sm_count() {
+    if (g_sm_count == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            g_sm_count <= 0)
+            g_sm_count = 148;  // B200
+    }
+    return g_sm_count;
+}
+
+int zblocks_of(int q_heads, int kv_heads, int rows) { return (rows * (q_heads / kv_heads) + kRows - 1) / kRows; }
+
+// Splits over the sealed pages: one CTA per SM in total, the open-tile CTAs included, at least one
+// page per warp where the context is long enough.
+int split_count(int kv_len_max, int kv_heads, int zblocks) {
+    const int pages = 2 * (kv_len_max / kTile);
+    const int per = kv_heads * zblocks;
+    int n = (sm_count() - per) / per;
+    n = n < 1 ? 1 : n;
+    const int by_pages = (pages + 1) / 2;  // at least two pages per CTA
+    if (n > by_pages) n = by_pages;
+    return n < 1 ? 1 : n;
+}
+
+}  // namespace
+}  // namespace kvb
+
+namespace kvb {
+namespace {
+
+int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_dev, const int32_t* total_pos_dev, int T,
+                     float scale, int kv_len_max,
+                     int key_begin, int key_end, void* workspace, void* out, float* part_m, float* part_l,
+                     float* part_o, cudaStream_t stream, const char* who) {
+    if (int st = check_layer(layer, who)) return st;
+    if (q == nullptr || pos_dev == nullptr || workspace == nullptr) return fail(KVB_EINVAL, "%s: null q / positions / workspace", who);
+    if (out == nullptr && part_m == nullptr) return fail(KVB_EINVAL, "%s: null output", who);
+    if (T < 1 || T > 8) return fail(KVB_ERANGE, "%s: %d query tokens (1..8 supported)", who, T);
+    if (kv_len_max < 1) return fail(KVB_EINVAL, "%s: kv_len_max %d", who, kv_len_max);
+    if (layer->head_dim != 128) return fail(KVB_ERANGE, "%s: head_dim %d (the fused attention kernels cover 128)", who, layer->head_dim);
+    if (layer->sinkhorn_iters != 0)
+        return fail(KVB_ERANGE, "%s: sinkhorn_iters %d (the fused attention kernels cover the iters = 0 cache)", who, layer->sinkhorn_iters);
+    if (layer->stage == nullptr) return fail(KVB_EINVAL, "%s: layer has no stage buffer", who);
+    const int Z = zblocks_of(layer->q_heads, layer->kv_heads, T);
+    const int nsplit = split_count(kv_len_max, layer->kv_heads, Z);
+    const int parts = nsplit + 1;
+    AttnParams P;
+    P.L = make_view(*layer);
+    P.q = static_cast<const uint16_t*>(q);
+    P.pos = pos_dev;
+    P.total_pos = total_pos_dev;
+    P.T = T;
+    P.scale_log2 = scale * 1.4426950408889634f;
+    P.nsplit = nsplit;
+    P.key_begin = key_begin;
+    P.key_end = key_end;
+    const size_t rows = static_cast<size_t>(layer->kv_heads) * Z * parts * kRows;
+    P.ws_m = static_cast<float*>(workspace);
+    P.ws_l = P.ws_m + rows;
+    P.ws_o = P.ws_l + rows;
+    const bool upper = T * (layer->q_heads / layer->kv_heads) > 8;
+    const int smem = static_cast<int>(sizeof(AttnSmem));
+    static bool opted = false;
+    if (!opted) {
+        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        opted = true;
+    }
+    const dim3 grid(parts, layer->kv_heads, Z);
+    if (upper) attn_kernel<true, false><<<grid, kThreads, smem, stream>>>(P);
+    else attn_kernel<false, false><<<grid, kThreads, smem, stream>>>(P);
+    KVB_CUDA_OK(cudaGetLastError());
+    const int total_rows = T * layer->q_heads;
+    reduce_kernel<<<(total_rows + 3) / 4, 128, 0, stream>>>(P.ws_m, P.ws_l, P.ws_o, parts, T, layer->q_heads, layer->kv_heads, Z,
+                                                            layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o);
+    KVB_CUDA_OK(cudaGetLastError());
+    return KVB_OK;
+}
+
+}  // namespace
+}  // namespace kvb
+
+extern "C" int kvb_split_capacity(int kv_len_max, int kv_heads, int q_heads, int rows, int batch) {
+    (void)batch;
+    if (kv_heads < 1 || q_heads < kv_heads || rows < 1) return 0;
+    return kvb::split_count(kv_len_max, kv_heads, kvb::zblocks_of(q_heads, kv_heads, rows)) + 1;
+}
+
+extern "C" size_t kvb_workspace_bytes(int kv_len_max, int kv_heads, int q_heads, int head_dim, int rows, int batch) {
+    if (kv_heads < 1 || q_heads < kv_heads || rows < 1 || batch < 1) return 0;
+    const int Z = kvb::zblocks_of(q_heads, kv_heads, rows);
+    const size_t parts = kvb::split_count(kv_len_max, kv_heads, Z) + 1;
+    return static_cast<size_t>(batch) * kv_heads * Z * parts * kvb::kRows * (head_dim + 2) * sizeof(float);
+}
+
+extern "C" int kvb_attn_decode(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
+                               void* workspace, void* out, void* stream) {
+    return kvb::launch_attention(layer, q, pos_dev, pos_dev, 1, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr, nullptr,
+                                 static_cast<cudaStream_t>(stream), "kvb_attn_decode");
+}
+
+extern "C" int kvb_attn_decode_partial(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale,
+                                       int kv_len_max, int key_begin, int key_end, void* workspace, float* part_m,
+                                       float* part_l, float* part_o, void* stream) {
+    if (part_m == nullptr || part_l == nullptr || part_o == nullptr)
+        return kvb::fail(KVB_EINVAL, "kvb_attn_decode_partial: null partial output");
+    return kvb::launch_attention(layer, q, pos_dev, pos_dev, 1, scale, kv_len_max, key_begin, key_end, workspace, nullptr, part_m, part_l,
+                                 part_o, static_cast<cudaStream_t>(stream), "kvb_attn_decode_partial");
+}
+
+extern "C" int kvb_merge_partials(const float* parts_m, const float* parts_l, const float* parts_o, int parts, int q_heads,
+                                  int head_dim, int dtype, void* out, void* stream) {
+    using namespace kvb;
+    if (parts_m == nullptr || parts_l == nullptr || parts_o == nullptr || out == nullptr)
+        return fail(KVB_EINVAL, "kvb_merge_partials: null argument");
+    if (parts < 1 || q_heads < 1) return fail(KVB_EINVAL, "kvb_merge_partials: parts %d / q_heads %d", parts, q_heads);
+    if (head_dim != 128) return fail(KVB_ERANGE, "kvb_merge_partials: head_dim %d (128 supported)", head_dim);
+    merge_kernel<<<(q_heads + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(parts_m, parts_l, parts_o, parts, q_heads, dtype,
+                                                                                  static_cast<uint16_t*>(out));
+    KVB_CUDA_OK(cudaGetLastError());
+    return KVB_OK;
+}
+
+extern "C" int kvb_attn_verify(const kvb_layer* layer, const void* q, const void* k, const void* v,
+                               const int32_t* positions_dev, int width, float scale, int kv_len_max, void* workspace,
+                               void* out, void* stream) {
+    if (width < 1 || width > 8) return kvb::fail(KVB_ERANGE, "kvb_attn_verify: width %d (1..8; the reference rejects more, too)", width);
+    if (int st = kvb_append(layer, k, v, positions_dev, width, stream)) return st;
+    return kvb::launch_attention(layer, q, positions_dev, positions_dev + (width - 1), width, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr,
+                                 nullptr, static_cast<cudaStream_t>(stream), "kvb_attn_verify");
+}
+
+// First version of the prefill-chunk attention: quantise-append the chunk, then run the split-K kernel
+// over groups of 8 query tokens.  Correct for any chunk, but every group streams the whole prefix again.
+extern "C" size_t kvb_prefill_workspace_bytes(int kv_len_max, int kv_heads, int q_heads, int head_dim, int tokens) {
+    (void)tokens;
+    return kvb_workspace_bytes(kv_len_max, kv_heads, q_heads, head_dim, 8, 1);
+}
+
+extern "C" int kvb_attn_prefill(const kvb_layer* layer, const void* q, const void* k, const void* v,
+                                const int32_t* positions_dev, int tokens, float scale, int kv_len_max, void* workspace,
+                                void* out, void* stream) {
+    if (tokens < 1) return kvb::fail(KVB_EINVAL, "kvb_attn_prefill: tokens = %d", tokens);
+    if (int st = kvb_append(layer, k, v, positions_dev, tokens, stream)) return st;
+    const size_t row_bytes = static_cast<size_t>(layer->q_heads) * layer->head_dim * 2;
+    for (int t0 = 0; t0 < tokens; t0 += 8) {
+        const int w = tokens - t0 < 8 ? tokens - t0 : 8;
+        const int st = kvb::launch_attention(layer, static_cast<const char*>(q) + t0 * row_bytes, positions_dev + t0,
+                                             positions_dev + (tokens - 1), w, scale, kv_len_max, 0, INT_MAX, workspace,
+                                             static_cast<char*>(out) + t0 * row_bytes, nullptr, nullptr, nullptr,
+                                             static_cast<cudaStream_t>(stream), "kvb_attn_prefill");
+        if (st) return st;
+    }
+    return KVB_OK;
+}

@@ -1,0 +1,68 @@
+"""CPU tests of the boundary: the library loads, exports every symbol the header declares, and rejects bad
+arguments on the host before any launch (no GPU needed for these paths)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from helpers import ROOT, pkg
+
+
+def test_library_exports_every_declared_symbol():
+    p = pkg()
+    p.build()
+    lib = p.capi.load()
+    header = open(os.path.join(ROOT, "include", "kvarn_b200.h")).read()
+    declared = set(re.findall(r"\b(kvb_[a-z_0-9]+)\s*\(", header))
+    declared -= {"kvb_status", "kvb_layer"}
+    assert declared, "no declarations found"
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    assert set(p.capi.SYMBOLS) == declared
+
+
+def test_sizes():
+    lib = pkg().capi.load()
+    assert lib.kvb_stage_bytes(128, 4) == 2 * 2 * 4 * 128 * 128 * 2
+    assert lib.kvb_stage_bytes(256, 4) == 1 << 20
+    assert [lib.kvb_plane_bytes(w, 128, 4, 2) for w in range(4)] == [4096 * 8, 640 * 8, 4096 * 8, 512 * 8]
+    assert [lib.kvb_plane_bytes(w, 256, 1, 1) for w in range(4)] == [8192, 1280, 8192, 1024]
+    assert lib.kvb_split_capacity(32768, 4, 24, 1, 1) >= 2
+    assert lib.kvb_workspace_bytes(32768, 4, 24, 128, 1, 1) > 0
+
+
+def _layer(capi, **over):
+    L = capi.kvb_layer(k_code=16, k_scale=16, v_code=16, v_scale=16, stage=16, table_direct=16, tables=None,
+                       table_rows=None, table_stride=0, table_len=4, pages=4, kv_heads=4, q_heads=24, head_dim=128,
+                       dtype=0, sinkhorn_iters=0, error_word=None)
+    for k, v in over.items():
+        setattr(L, k, v)
+    return L
+
+
+@pytest.mark.parametrize("over", [dict(kv_heads=0), dict(kv_heads=9), dict(head_dim=64), dict(q_heads=25), dict(dtype=3),
+                                  dict(k_code=None), dict(table_direct=None), dict(pages=0), dict(sinkhorn_iters=-1)])
+def test_bad_layer_is_rejected_on_the_host(over, capfd):
+    capi = pkg().capi
+    lib = capi.load()
+    L = _layer(capi, **over)
+    st = lib.kvb_append(C.byref(L), 16, 16, 16, 1, None)
+    assert st == capi.KVB_EINVAL
+    assert lib.kvb_last_error_string()
+    assert "kvarn_b200:" in capfd.readouterr().err  # loud failure, like the reference's fprintf before it throws
+
+
+def test_null_arguments_and_ranges():
+    capi = pkg().capi
+    lib = capi.load()
+    L = _layer(capi)
+    assert lib.kvb_append(C.byref(L), None, 16, 16, 1, None) == capi.KVB_EINVAL
+    assert lib.kvb_append(C.byref(L), 16, 16, 16, 0, None) == capi.KVB_OK  # empty append: silent no-op
+    assert lib.kvb_append(C.byref(L), 16, 16, 16, -1, None) == capi.KVB_EINVAL
+    assert lib.kvb_decode_tile(C.byref(L), 5, 0, 16, 16, None) == capi.KVB_EINVAL
+    assert lib.kvb_attn_decode(C.byref(L), None, 16, 0.1, 128, 16, 16, None) == capi.KVB_EINVAL
+    assert lib.kvb_attn_verify(C.byref(L), 16, 16, 16, 16, 9, 0.1, 128, 16, 16, None) == capi.KVB_ERANGE
+    assert lib.kvb_merge_partials(None, 16, 16, 2, 24, 128, 0, 16, None) == capi.KVB_EINVAL
+    with pytest.raises(capi.KvarnError):
+        capi.check(capi.KVB_EINVAL)

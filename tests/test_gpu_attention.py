@@ -1,0 +1,158 @@
+"""GPU parity of the fused attention kernels (decode, MTP verify, partial + merge, prefill chunk) against the
+CPU oracle: softmax attention in double precision over the de-quantised cache.  Tolerance: see helpers."""
+import numpy as np
+import pytest
+
+from helpers import Twin, attn_close, orc, pkg
+
+pytestmark = pytest.mark.gpu
+
+
+def _decode(tw, q16, pos):
+    import torch
+
+    qd = torch.from_numpy(q16).to(tw.dev)
+    p = torch.tensor([pos], dtype=torch.int32, device=tw.dev)
+    out = tw.gpu.attn_decode(qd, p, 1.0 / np.sqrt(tw.D), pos + 1)
+    torch.cuda.synchronize()
+    return out.float().cpu().numpy()
+
+
+def test_config0_decode_at_4096():
+    tw = Twin(D=128, H=4, QH=24, capacity_tokens=4096, seed=0)
+    k, v = orc.synth_kv(0, 4096, 4, 128, 1), orc.synth_kv(0, 4096, 4, 128, 2)
+    tw.append(k, v)
+    q = orc.synth_q(0, 1, 24, 128)
+    want = tw.cpu.attention(q, [4095], 1.0 / np.sqrt(128), 24, threads=8)
+    got = _decode(tw, q[0], 4095)
+    ok, msg = attn_close(got, want[0])
+    assert ok, msg
+    assert tw.gpu.errors() == 0
+
+
+@pytest.mark.parametrize("T", [1, 15, 16, 51, 64, 127, 128, 129, 191, 192, 300, 1000, 2049])
+def test_decode_ragged_lengths(T):
+    tw = Twin(D=128, H=4, QH=24, capacity_tokens=T, seed=T)
+    k, v = orc.synth_kv(T, T, 4, 128, 1), orc.synth_kv(T, T, 4, 128, 2)
+    tw.append(k, v)
+    q = orc.synth_q(T, 1, 24, 128)
+    want = tw.cpu.attention(q, [T - 1], 1.0 / np.sqrt(128), 24, threads=4)
+    got = _decode(tw, q[0], T - 1)
+    ok, msg = attn_close(got, want[0])
+    assert ok, msg
+
+
+@pytest.mark.parametrize("H,QH", [(4, 4), (2, 16), (1, 7), (8, 8)])
+def test_decode_other_head_shapes(H, QH):
+    T = 700
+    tw = Twin(D=128, H=H, QH=QH, capacity_tokens=T, seed=21)
+    k, v = orc.synth_kv(22, T, H, 128, 1), orc.synth_kv(22, T, H, 128, 2)
+    tw.append(k, v)
+    q = orc.synth_q(22, 1, QH, 128)
+    want = tw.cpu.attention(q, [T - 1], 1.0 / np.sqrt(128), QH, threads=4)
+    ok, msg = attn_close(_decode(tw, q[0], T - 1), want[0])
+    assert ok, msg
+
+
+def test_decode_bf16_io():
+    import torch
+
+    T = 900
+    tw = Twin(D=128, H=4, QH=24, capacity_tokens=T, seed=23, dtype=1)
+    k, v = orc.synth_kv(24, T, 4, 128, 1), orc.synth_kv(24, T, 4, 128, 2)
+    tw.append(k, v)
+    from helpers import from_bits, to_bits
+    qb = to_bits(orc.synth_q(24, 1, 24, 128), 1)
+    want = tw.cpu.attention(qb, [T - 1], 1.0 / np.sqrt(128), 24, dtype=1, threads=4)
+    out = tw.gpu.attn_decode(from_bits(qb[0], 1).to(tw.dev), torch.tensor([T - 1], dtype=torch.int32, device=tw.dev),
+                             1.0 / np.sqrt(128), T)
+    got = out.float().cpu().numpy()
+    err = np.abs(got - want[0]).max()
+    assert err <= 2.0 ** -8 * np.abs(want).max(), err  # bf16 output rounding dominates
+
+
+@pytest.mark.parametrize("prefix,width", [(300, 1), (300, 4), (1000, 8), (125, 6), (120, 8), (127, 2), (0, 5)])
+def test_verify_rows_are_causal(prefix, width):
+    """Append width new rows then attend; covers verify steps that complete a tile (prefix 125 + 6, 120 + 8)."""
+    import torch
+
+    H, QH, D = 4, 24, 128
+    T = prefix + width
+    tw = Twin(D=D, H=H, QH=QH, capacity_tokens=T, seed=31)
+    k, v = orc.synth_kv(32, T, H, D, 1), orc.synth_kv(32, T, H, D, 2)
+    if prefix:
+        tw.append(k[:prefix], v[:prefix])
+    q = orc.synth_q(32, width, QH, D)
+    pos = np.arange(prefix, T, dtype=np.int32)
+    tw.cpu.append(k[prefix:], v[prefix:], prefix)
+    want = tw.cpu.attention(q, pos, 1.0 / np.sqrt(D), QH, threads=4)
+    out = tw.gpu.attn_verify(torch.from_numpy(q).to(tw.dev), torch.from_numpy(k[prefix:]).to(tw.dev),
+                             torch.from_numpy(v[prefix:]).to(tw.dev), torch.from_numpy(pos).to(tw.dev), 1.0 / np.sqrt(D), T)
+    torch.cuda.synchronize()
+    tw.len = T
+    eq = tw.planes_equal()
+    assert all(eq.values()), eq
+    ok, msg = attn_close(out.float().cpu().numpy(), want)
+    assert ok, msg
+
+
+def test_partials_merge_to_the_full_answer():
+    """Key ranges attended separately and merged by log-sum-exp (what the multi-GPU combine does)."""
+    import torch
+
+    T = 1500
+    tw = Twin(D=128, H=4, QH=24, capacity_tokens=T, seed=41)
+    k, v = orc.synth_kv(42, T, 4, 128, 1), orc.synth_kv(42, T, 4, 128, 2)
+    tw.append(k, v)
+    q = orc.synth_q(42, 1, 24, 128)
+    scale = 1.0 / np.sqrt(128)
+    want, wm, wl, wo = tw.cpu.attention(q, [T - 1], scale, 24, threads=4, want_partials=True)
+    qd = torch.from_numpy(q[0]).to(tw.dev)
+    pos = torch.tensor([T - 1], dtype=torch.int32, device=tw.dev)
+    cuts = [0, 200, 640, 1283, T]
+    ms, ls, os_ = [], [], []
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        m, l, o = tw.gpu.attn_decode_partial(qd, pos, scale, T, a, b)
+        ms.append(m); ls.append(l); os_.append(o)
+        cm, cl, co = tw.cpu.attention(q, [T - 1], scale, 24, key_begin=a, key_end=b, want_partials=True)[1:]
+        # compare normalised partial outputs (m, l individually depend on the split, their combination does not)
+        assert np.allclose(m.cpu().numpy() + np.log(l.cpu().numpy()), cm[0] + np.log(cl[0]), atol=2e-3)
+    merged = pkg().merge_partials(torch.stack(ms), torch.stack(ls), torch.stack(os_))
+    ok, msg = attn_close(merged.float().cpu().numpy(), want[0])
+    assert ok, msg
+    full = tw.gpu.attn_decode(qd, pos, scale, T)
+    ok, msg = attn_close(full.float().cpu().numpy(), want[0])
+    assert ok, msg
+
+
+def test_prefill_chunk_small():
+    import torch
+
+    H, QH, D, prefix, chunk = 4, 24, 128, 333, 100
+    T = prefix + chunk
+    tw = Twin(D=D, H=H, QH=QH, capacity_tokens=T, seed=51)
+    k, v = orc.synth_kv(52, T, H, D, 1), orc.synth_kv(52, T, H, D, 2)
+    tw.append(k[:prefix], v[:prefix])
+    q = orc.synth_q(52, chunk, QH, D)
+    pos = np.arange(prefix, T, dtype=np.int32)
+    tw.cpu.append(k[prefix:], v[prefix:], prefix)
+    want = tw.cpu.attention(q, pos, 1.0 / np.sqrt(D), QH, threads=8)
+    out = tw.gpu.attn_prefill(torch.from_numpy(q).to(tw.dev), torch.from_numpy(k[prefix:]).to(tw.dev),
+                              torch.from_numpy(v[prefix:]).to(tw.dev), torch.from_numpy(pos).to(tw.dev), 1.0 / np.sqrt(D), T)
+    torch.cuda.synchronize()
+    ok, msg = attn_close(out.float().cpu().numpy(), want)
+    assert ok, msg
+
+
+def test_bad_page_id_is_reported_not_faulted():
+    import torch
+
+    T = 600
+    tw = Twin(D=128, H=4, QH=24, capacity_tokens=T, seed=61)
+    k, v = orc.synth_kv(62, T, 4, 128, 1), orc.synth_kv(62, T, 4, 128, 2)
+    tw.append(k, v)
+    tw.gpu.table[3] = -7
+    q = orc.synth_q(62, 1, 24, 128)
+    out = _decode(tw, q[0], T - 1)
+    assert np.isfinite(out).all()
+    assert tw.gpu.errors() & pkg().capi.ERR_PAGE_RANGE
