@@ -15,7 +15,8 @@ from .build import build  # noqa: F401
 
 def __getattr__(name):
     if name in ("KvarnLayer", "merge_partials", "default_scale", "cache"):
-        from . import cache
+        import importlib
 
+        cache = importlib.import_module(__name__ + ".cache")
         return cache if name == "cache" else getattr(cache, name)
     raise AttributeError(name)
