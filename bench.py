@@ -1,0 +1,333 @@
+#!/usr/bin/env python3
+"""Benchmark of the KVarN quantized-KV decode hot path on B200.
+
+Workload at every N (one process per GPU, no data-path collective, weak scaling): batch-1 decode at a
+32,768-token context across 16 attention layers, 24 query heads / 4 KV heads / head_dim 128, seed-shuffled
+page table of 64-token pages per layer.  One step = for each layer: append 1 new token (rotate + stage,
+sealing a tile every 128 steps), then one decode query over the whole cache.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N ...            # the CPU path (oracle port) on the host cores
+
+Prints ONE JSON line (rank 0).  `value` = algorithmic HBM bytes per step / device time with inputs resident
+in HBM; `e2e` = the same through the C ABI with host buffers (H2D of q/k/v, D2H of the outputs, per step).
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D, H, QH, LAYERS, CTX = 128, 4, 24, 16, 32768
+SEALED_B, TAIL_B = 140, 512  # algorithmic bytes per sealed / open-tile token per KV head (codes + 12 B of axes | fp16 K+V rows)
+
+
+def decode_bytes(kv_len: int) -> int:
+    """Algorithmic bytes one decode call must move: codes and axes of every sealed token, fp16 rows of the
+    open tile, q in, out back, one page id per page."""
+    sealed = (kv_len // 128) * 128
+    return sealed * H * SEALED_B + (kv_len - sealed) * H * TAIL_B + 2 * QH * D * 2 + 4 * ((kv_len + 63) // 64)
+
+
+def append_bytes(tokens: int) -> int:
+    """Rows read (K and V) + the same rows written to the stage."""
+    return 2 * tokens * H * D * 2 * 2
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def cpu_threads():
+    return os.cpu_count() or 1
+
+
+def cpu_decode_sample(cpu_layer, q16, pos, threads, reps):
+    """Times the oracle port's decode attention (one layer at the bench context) on the host cores."""
+    best = None
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        out = cpu_layer.attention(q16, [pos], 1.0 / math.sqrt(D), QH, threads=threads)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best, out
+
+
+def run_reference(args):
+    """The CPU path: oracle port of append + decode attention, all host threads, one layer per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import kvarn_oracle as orc
+
+    orc.build()
+    threads = cpu_threads()
+    lp = CTX // 64 + 4
+    table = orc.shuffled_table(0, lp, lp + 2)
+    layer = orc.CpuLayer(D, H, lp + 2, table)
+    k, v = orc.synth_kv(0, CTX + 64, H, D, 1), orc.synth_kv(0, CTX + 64, H, D, 2)
+    layer.append(k[:CTX], v[:CTX], 0)
+    q = orc.synth_q(0, 1, QH, D)
+    pos = CTX
+    times = []
+    for s in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        layer.append(k[pos:pos + 1], v[pos:pos + 1], pos)
+        layer.attention(q, [pos], 1.0 / math.sqrt(D), QH, threads=threads)
+        dt = time.perf_counter() - t0
+        if s >= args.warmup:
+            times.append(dt)
+        pos += 1
+    per_layer = sum(times) / len(times)
+    nbytes = decode_bytes(CTX + 1) + append_bytes(1)
+    gbs = nbytes / per_layer / 1e9
+    sample = f"1 of {LAYERS} layers per step (append 1 token + decode at {CTX}), oracle port, {threads} threads"
+    print(json.dumps({
+        "impl": "reference", "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_layer * LAYERS * 1e3, "us_per_layer": per_layer * 1e6,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": config_dict(args.gpus),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def config_dict(n):
+    return {"workload": "decode_ctx32768_16layers_b1 (BASELINE config 1), one sequence per GPU", "layers": LAYERS, "ctx": CTX,
+            "q_heads": QH, "kv_heads": H, "head_dim": D, "page_tokens": 64, "kv_format": "kvarn128 K4V4 iters0 (P1 planes)",
+            "parallelism": f"dp{n} (sequences sharded, no collective)",
+            "l2": "16 layers x 19 MB of KV per step exceed the 126 MB L2; no explicit flush"}
+
+
+def run_gpu(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import __graft_entry__ as entry
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = entry.load_package()
+    pkg.capi.load()  # fails loudly when the CUDA library is missing: there is no fallback
+    from oracle import kvarn_oracle as orc  # checker + cpu_baseline leg only
+
+    scale = 1.0 / math.sqrt(D)
+    total_steps = args.warmup + 3 * args.steps + 8
+    kv_len_max = CTX + total_steps + 1
+    lp = (kv_len_max + 63) // 64 + 2
+    lp += lp & 1
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1000 * rank)
+
+    def synth(tokens, heads):
+        x = torch.randn((tokens, heads, D), generator=gen, device=dev, dtype=torch.float32)
+        x[..., [3, 17, 64, 101]] *= 20.0
+        return x.to(torch.float16)
+
+    layers = []
+    for li in range(LAYERS):
+        table = torch.from_numpy(orc.shuffled_table(100 * rank + li, lp, lp))
+        L = pkg.KvarnLayer(D, H, QH, lp, table, device=str(dev))
+        for c0 in range(0, CTX, 4096):  # prefill by appends
+            L.append(synth(4096, H), synth(4096, H), torch.arange(c0, c0 + 4096, dtype=torch.int32, device=dev))
+        layers.append(L)
+    # per-step inputs (resident): one q/k/v set per layer, replayed every step; only the position advances
+    qkv = torch.empty((LAYERS, QH + 2 * H, D), dtype=torch.float16, device=dev)
+    qkv[:, :QH] = torch.randn((LAYERS, QH, D), generator=gen, device=dev).to(torch.float16)
+    qkv[:, QH:] = synth(LAYERS, 2 * H)
+    outs = torch.empty((LAYERS, QH, D), dtype=torch.float16, device=dev)
+    pos = torch.full((1,), CTX, dtype=torch.int32, device=dev)
+    for L in layers:
+        L.workspace(kv_len_max, 1)
+    torch.cuda.synchronize()
+
+    def step_body():
+        for li, L in enumerate(layers):
+            L.append(qkv[li, QH:QH + H].unsqueeze(0), qkv[li, QH + H:].unsqueeze(0), pos)
+            L.attn_decode(qkv[li, :QH], pos, scale, kv_len_max, out=outs[li])
+        pos.add_(1)
+
+    def decode_only_body():
+        for li, L in enumerate(layers):
+            L.attn_decode(qkv[li, :QH], pos_fixed, scale, kv_len_max, out=outs[li])
+
+    step_body()  # warm every kernel once outside capture (function attributes are set on first use)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(device=dev)
+    g_step, g_dec = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g_step, stream=side):
+        step_body()
+    pos_fixed = torch.full((1,), CTX, dtype=torch.int32, device=dev)
+    with torch.cuda.graph(g_dec, stream=side):
+        decode_only_body()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        g_step.replay()
+    with ClockSampler(local) as clk:
+        ms_step = timed(g_step.replay, args.steps) / args.steps
+        # decode-only graph: the dominant kernel in isolation (16 layers x 19 MB > L2 between revisits)
+        for _ in range(3):
+            g_dec.replay()
+        ms_dec = timed(g_dec.replay, args.steps) / args.steps
+        # end to end: host buffers in, host buffers out, every step
+        h_in = torch.empty_like(qkv, device="cpu").pin_memory()
+        h_in.copy_(qkv)
+        h_out = torch.empty_like(outs, device="cpu").pin_memory()
+
+        def e2e_step():
+            qkv.copy_(h_in, non_blocking=True)
+            g_step.replay()
+            h_out.copy_(outs, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        ms_e2e = timed(e2e_step, args.steps) / args.steps
+    clocks = clk.summary()
+
+    cur = int(pos.item())  # context after all steps
+    step_bytes = LAYERS * (decode_bytes(cur) + append_bytes(1))
+    dec_bytes = decode_bytes(CTX + 1)
+    peak, peak_kind = peaks()
+    value = world * step_bytes / (ms_step * 1e-3) / 1e9
+    e2e = world * step_bytes / (ms_e2e * 1e-3) / 1e9
+    achieved = dec_bytes / (ms_dec * 1e-3 / LAYERS) / 1e9
+
+    result = None
+    if rank == 0:
+        # parity at full size + CPU baseline on a bounded sample: one layer's decode on the host cores
+        L0 = layers[0]
+        cpu = orc.CpuLayer(D, H, lp, L0.table.cpu().numpy())
+        cpu.k_code[:] = L0.k_code.cpu().numpy(); cpu.v_code[:] = L0.v_code.cpu().numpy()
+        cpu.k_scale[:] = L0.k_scale.cpu().numpy().view(np.uint16); cpu.v_scale[:] = L0.v_scale.cpu().numpy().view(np.uint16)
+        cpu.stage[:] = L0.stage.cpu().numpy().view(np.uint16).reshape(cpu.stage.shape)
+        cpu.kv_total = cur
+        pos_chk = torch.full((1,), cur - 1, dtype=torch.int32, device=dev)
+        got = L0.attn_decode(qkv[0, :QH], pos_chk, scale, kv_len_max).float().cpu().numpy()
+        threads = cpu_threads()
+        t_cpu, want = cpu_decode_sample(cpu, qkv[0, :QH].cpu().numpy(), cur - 1, threads, reps=3)
+        err = float(np.abs(got - want[0]).max() / np.abs(want).max())
+        result = {
+            "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3 / LAYERS,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": config_dict(world),
+            "pct_of_hbm_peak": 100.0 * value / world / peak,
+            "roofline": {"bound": "hbm", "kernel": "attn_kernel (+ reduce_kernel, timed together)", "achieved": achieved,
+                         "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "us_per_launch": ms_dec * 1e3 / LAYERS, "algorithmic_bytes_per_launch": dec_bytes},
+            "cpu_baseline": {"value": decode_bytes(cur) / t_cpu / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                             "sample": f"decode attention of 1 of {LAYERS} layers at {cur} tokens, best of 3, oracle port"},
+            "e2e": {"value": e2e, "unit": "GB/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": world * qkv.numel() * 2,
+                    "d2h_bytes_per_step": world * outs.numel() * 2},
+            "gpu_launches": args.steps * LAYERS * 3,
+            "parity": {"max_abs_over_ref_max": err, "checked": f"layer 0 decode at {cur} tokens vs CPU oracle"},
+            "clocks": clocks,
+        }
+        tr = os.path.join(ROOT, "profiles", "attn_kernel_traffic.json")
+        if os.path.exists(tr):
+            result["roofline"]["traffic"] = json.load(open(tr)).get("dram_bytes_per_launch_at_bench_size")
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

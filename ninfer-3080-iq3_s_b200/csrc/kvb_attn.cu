@@ -12,10 +12,13 @@
 //   logit[r][j] = other_K[j] * ( sum_d (q'[r][d] * scale_K[d]) * code_K[j][d]  +  sum_d q'[r][d] * zp_K[d] )
 //   o[r][d]    += other_V[d] * ( sum_j (p[r][j] * scale_V[j]) * code_V[j][d]  +  sum_j p[r][j] * zp_V[j] )
 // with q' = H q * softmax_scale * log2(e).  The two contractions run on the warp-level tensor cores
-// (m16n8k16, fp16 operands, fp32 accumulate): 4-bit codes are exact in fp16, q' * scale_K is split into
-// an fp16 high and low part so the product keeps fp32 accuracy, and p * scale_V is rounded to fp16 once.
-// Codes are unpacked with one logic op per pair (see unpack8); V pairs are formed across two tokens with
-// a byte permute so that no transpose through shared memory is needed.
+// (m16n8k16, fp16 operands, fp32 accumulate) with the KEYS (QK) and the DIMS (PV) on the 16-wide M side and
+// the GQA-merged query rows on the 8-wide N side, so six query heads waste a quarter of a tile, not five
+// eighths: S^T[key][row] = K_codes . (q' scale_K)^T and O^T[dim][row] = V_codes^T . (p scale_V)^T.
+// 4-bit codes are exact in fp16, q' * scale_K is split into an fp16 high and low part so the product keeps
+// fp32 accuracy, and p * scale_V is rounded to fp16 once.  Codes are unpacked with one logic op per pair
+// (see unpack8); V pairs are formed across two keys with a byte permute and the probabilities change from
+// accumulator to operand layout with one movmatrix per 8 keys, so nothing is transposed through memory.
 #include <climits>
 
 #include "kvb_common.cuh"
@@ -27,7 +30,7 @@ namespace {
 constexpr int D = 128;
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kRows = 16;  // query rows per CTA (one MMA M block)
+constexpr int kRows = 16;  // query rows per CTA: one or two 8-row N blocks
 constexpr int kKCodeOff = 0, kVCodeOff = 4096, kKScaleOff = 8192, kVScaleOff = 8832, kPageBytes = 9344;
 constexpr int kSlots = 2;
 constexpr int kScratchBytes = 256 + 256 + 128;  // per warp: scale_K[128], zp_K[128], other_K[64] as fp16
@@ -55,31 +58,42 @@ struct __align__(16) AttnSmem {
     int row_pos[kRows];
 };
 
-// Per-thread state of the running softmax for rows g (index 0) and g + 8 (index 1).
-struct Acc {
-    float o[16][4];  // PV accumulators: n-block nb holds dims 32t+nb (c0/c2) and 32t+16+nb (c1/c3)
-    float m[2], l[2], z[2];
+// Per-thread state of the running softmax.  Lane (g, t) owns query rows 8 nb + 2t, 2t+1 of n-block nb and,
+// in the PV accumulators, dims 16g .. 16g+15: o[nb][mb] = {(dim 16g+mb, row 2t), (dim 16g+mb, row 2t+1),
+// (dim 16g+8+mb, row 2t), (dim 16g+8+mb, row 2t+1)}.  l and z are partial over the lane's keys.
+template <int NB> struct Acc {
+    float o[NB][8][4];
+    float m[NB][2], l[NB][2], z[NB][2];
 };
 
-struct QFrag {
-    uint32_t hi[8][4];  // A fragments of q' * scale_K, per k-block: a0 a1 a2 a3
-    uint32_t lo[8][4];
-    float qz[2];        // sum_d q'[row][d] * zp_K[d]
+// B fragments of (q' * scale_K)^T per n-block and k-block (b0, b1), high and low fp16 parts, and
+// qz = sum_d q'[row][d] * zp_K[d] for the lane's two rows.
+template <int NB> struct QFrag {
+    uint32_t hi[NB][8][2];
+    uint32_t lo[NB][8][2];
+    float qz[NB][2];
 };
 
-// Build the A fragments for one tile from q' (shared memory, fragment order) and the tile's per-dim
-// scale / zero point (warp scratch, natural dim order).  k-slot pairing follows unpack8:
-// word i of the lane's 32-dim chunk feeds k-blocks 2i (dims +0,+4 | +1,+5) and 2i+1 (dims +2,+6 | +3,+7).
-template <bool kScaled>
-__device__ __forceinline__ void build_qfrag(const AttnSmem& sm, const uint8_t* scratch, int lane, QFrag& f) {
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
+    return r;
+}
+
+// Build the Q-side fragments for one tile from q' (shared memory, fragment order) and the tile's per-dim
+// scale / zero point (warp scratch, natural dim order).  Lane (g, t) prepares row 8 nb + g, dims
+// 32t .. 32t+31.  k-slot pairing follows unpack8: word i of the 32-dim chunk feeds k-blocks 2i (dims
+// +0,+4 | +1,+5) and 2i+1 (dims +2,+6 | +3,+7); un-quantised stage rows use natural pairs (2e, 2e+1).
+template <bool kScaled, int NB>
+__device__ __forceinline__ void build_qfrag(const AttnSmem& sm, const uint8_t* scratch, int lane, QFrag<NB>& f) {
     const int t = lane & 3;
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
+    for (int nb = 0; nb < NB; ++nb) {
         float qs[32];
         float qz = 0.0f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const float4 qv = sm.qfrag[hf][j][lane];
+            const float4 qv = sm.qfrag[nb][j][lane];
             if constexpr (kScaled) {
                 const uint2 ks = *reinterpret_cast<const uint2*>(scratch + (32 * t + 4 * j) * 2);
                 const uint2 kz = *reinterpret_cast<const uint2*>(scratch + 256 + (32 * t + 4 * j) * 2);
@@ -94,22 +108,19 @@ __device__ __forceinline__ void build_qfrag(const AttnSmem& sm, const uint8_t* s
             }
         }
         qz += __shfl_xor_sync(0xffffffffu, qz, 1);
-        qz += __shfl_xor_sync(0xffffffffu, qz, 2);
-        f.qz[hf] = qz;
+        qz += __shfl_xor_sync(0xffffffffu, qz, 2);  // every lane of group g now holds qz of row 8 nb + g
+        f.qz[nb][0] = __shfl_sync(0xffffffffu, qz, 8 * t);      // row 2t   lives in lanes 4 * (2t) ..
+        f.qz[nb][1] = __shfl_sync(0xffffffffu, qz, 8 * t + 4);  // row 2t+1 lives in lanes 4 * (2t+1) ..
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                // quantised pages: pairs (e, e+4) of word i.  stage rows (un-quantised): natural pairs (2e, 2e+1).
                 const float x0 = kScaled ? qs[8 * i + e] : qs[8 * i + 2 * e];
                 const float x1 = kScaled ? qs[8 * i + e + 4] : qs[8 * i + 2 * e + 1];
                 const uint32_t h = pack_half2(x0, x1);
                 const float2 hf32 = unpack_half2(h);
-                const uint32_t l = pack_half2(x0 - hf32.x, x1 - hf32.y);
-                // e = 0,1 -> k-block 2i (a0 | a2); e = 2,3 -> k-block 2i+1
-                const int kb = 2 * i + (e >> 1), reg = (e & 1) * 2 + hf;
-                f.hi[kb][reg] = h;
-                f.lo[kb][reg] = l;
+                f.hi[nb][2 * i + (e >> 1)][e & 1] = h;
+                f.lo[nb][2 * i + (e >> 1)][e & 1] = pack_half2(x0 - hf32.x, x1 - hf32.y);
             }
         }
     }
@@ -126,188 +137,195 @@ __device__ __forceinline__ void transpose_k_scale(const uint8_t* kscale_page, ui
     *reinterpret_cast<uint32_t*>(scratch + 512 + 4 * lane) = prmt(w2, w4, 0x7610);
 }
 
-// Online-softmax update of one 64-key block whose logits (log2 units) sit in s[8][4]
-// (n-block nbk = 2*grp + nb: c0,c1 = row g, keys 16grp + 8nb + 2t, +1; c2,c3 = row g+8).
+// Online-softmax update of NG groups of 16 keys whose logits (log2 units) sit in s[nb][grp][4]:
+// {(key g, row 2t), (key g, row 2t+1), (key g+8, row 2t), (key g+8, row 2t+1)} of group grp.
 // On return s holds p = exp2(logit - m_new); acc is rescaled if a row maximum moved.
-template <bool kUpper>
-__device__ __forceinline__ void softmax_block(float (&s)[8][4], Acc& acc) {
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int n = 0; n < 8; ++n) {
-        mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
-        if constexpr (kUpper) mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
-    }
-#pragma unroll
-    for (int hf = 0; hf < (kUpper ? 2 : 1); ++hf) {
-        mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
-        mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
-    }
-    float mnew[2], muse[2], alpha[2];
+template <int NB, int NG>
+__device__ __forceinline__ void softmax_block(float (&s)[NB][NG][4], Acc<NB>& acc) {
+    float muse[NB][2], alpha[NB][2];
     bool moved = false;
 #pragma unroll
-    for (int hf = 0; hf < (kUpper ? 2 : 1); ++hf) {
-        mnew[hf] = fmaxf(acc.m[hf], mx[hf]);
-        moved |= mnew[hf] > acc.m[hf];
-        muse[hf] = mnew[hf] == -INFINITY ? 0.0f : mnew[hf];
-        alpha[hf] = fast_exp2(acc.m[hf] - muse[hf]);
-        acc.m[hf] = mnew[hf];
+    for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float mx = -INFINITY;
+#pragma unroll
+            for (int grp = 0; grp < NG; ++grp) mx = fmaxf(mx, fmaxf(s[nb][grp][j], s[nb][grp][2 + j]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float mnew = fmaxf(acc.m[nb][j], mx);
+            moved |= mnew > acc.m[nb][j];
+            muse[nb][j] = mnew == -INFINITY ? 0.0f : mnew;
+            alpha[nb][j] = fast_exp2(acc.m[nb][j] - muse[nb][j]);
+            acc.m[nb][j] = mnew;
+        }
     }
     if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-        for (int n = 0; n < 16; ++n) {
-            acc.o[n][0] *= alpha[0]; acc.o[n][1] *= alpha[0];
-            if constexpr (kUpper) { acc.o[n][2] *= alpha[1]; acc.o[n][3] *= alpha[1]; }
-        }
-        acc.l[0] *= alpha[0]; acc.z[0] *= alpha[0];
-        if constexpr (kUpper) { acc.l[1] *= alpha[1]; acc.z[1] *= alpha[1]; }
-    }
+        for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-        s[n][0] = fast_exp2(s[n][0] - muse[0]); s[n][1] = fast_exp2(s[n][1] - muse[0]);
-        acc.l[0] += s[n][0] + s[n][1];
-        if constexpr (kUpper) {
-            s[n][2] = fast_exp2(s[n][2] - muse[1]); s[n][3] = fast_exp2(s[n][3] - muse[1]);
-            acc.l[1] += s[n][2] + s[n][3];
-        } else {
-            s[n][2] = 0.0f; s[n][3] = 0.0f;
+            for (int mb = 0; mb < 8; ++mb) {
+                acc.o[nb][mb][0] *= alpha[nb][0]; acc.o[nb][mb][1] *= alpha[nb][1];
+                acc.o[nb][mb][2] *= alpha[nb][0]; acc.o[nb][mb][3] *= alpha[nb][1];
+            }
+            acc.l[nb][0] *= alpha[nb][0]; acc.z[nb][0] *= alpha[nb][0];
+            acc.l[nb][1] *= alpha[nb][1]; acc.z[nb][1] *= alpha[nb][1];
         }
     }
-}
-
-// Key-position mask of a 64-key block starting at absolute position `first`.
-__device__ __forceinline__ void mask_block(float (&s)[8][4], int first, int lane, const int (&row_lim)[2], int key_begin,
-                                           int key_end) {
-    const int t = lane & 3;
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-        const int p0 = first + (n >> 1) * 16 + (n & 1) * 8 + 2 * t;
+    for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int p = p0 + (e & 1);
-            if (p > row_lim[e >> 1] || p < key_begin || p >= key_end) s[n][e] = -INFINITY;
+        for (int grp = 0; grp < NG; ++grp) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                s[nb][grp][e] = fast_exp2(s[nb][grp][e] - muse[nb][e & 1]);
+                acc.l[nb][e & 1] += s[nb][grp][e];
+            }
         }
     }
 }
 
 // One sealed page (64 keys) of one KV head, staged in shared memory at `pg`.
-template <bool kUpper, bool kOther>
-__device__ __forceinline__ void process_page(const uint8_t* pg, const uint8_t* scratch, const QFrag& qf, Acc& acc, int lane,
-                                             bool need_mask, int first_pos, const int (&row_lim)[2], int key_begin,
-                                             int key_end) {
+template <int NB, bool kOther>
+__device__ __forceinline__ void process_page(const uint8_t* pg, const uint8_t* scratch, const QFrag<NB>& qf, Acc<NB>& acc,
+                                             int lane, bool need_mask, int first_pos, const int (&row_lim)[NB][2],
+                                             int key_begin, int key_end) {
     const int g = lane >> 2, t = lane & 3;
-    float s[8][4];
-    // ---- QK: codes of 16 keys x 128 dims per group, two n-blocks of 8 keys
-#pragma unroll
-    for (int n = 0; n < 8; ++n) {
-        const int key = (n >> 1) * 16 + (n & 1) * 8 + g;
-        const uint4 kw = *reinterpret_cast<const uint4*>(pg + kKCodeOff + key * 64 + 16 * t);
-        const uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
-        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t u[4];
-            unpack8(w[i], u);
-            mma16816(c, qf.hi[2 * i][0], qf.hi[2 * i][1], qf.hi[2 * i][2], qf.hi[2 * i][3], u[0], u[1]);
-            mma16816(c, qf.hi[2 * i + 1][0], qf.hi[2 * i + 1][1], qf.hi[2 * i + 1][2], qf.hi[2 * i + 1][3], u[2], u[3]);
-            mma16816(c, qf.lo[2 * i][0], qf.lo[2 * i][1], qf.lo[2 * i][2], qf.lo[2 * i][3], u[0], u[1]);
-            mma16816(c, qf.lo[2 * i + 1][0], qf.lo[2 * i + 1][1], qf.lo[2 * i + 1][2], qf.lo[2 * i + 1][3], u[2], u[3]);
-        }
-        // keys of c0,c1 / c2,c3: 16grp + 8nb + 2t, +1
-        float o0 = 1.0f, o1 = 1.0f;
-        if constexpr (kOther) {
-            const float2 ko = unpack_half2(
-                *reinterpret_cast<const uint32_t*>(scratch + 512 + ((n >> 1) * 16 + (n & 1) * 8 + 2 * t) * 2));
-            o0 = ko.x; o1 = ko.y;
-        }
-        s[n][0] = (c[0] + qf.qz[0]) * o0; s[n][1] = (c[1] + qf.qz[0]) * o1;
-        s[n][2] = (c[2] + qf.qz[1]) * o0; s[n][3] = (c[3] + qf.qz[1]) * o1;
-    }
-    if (need_mask) mask_block(s, first_pos, lane, row_lim, key_begin, key_end);
-    softmax_block<kUpper>(s, acc);
-    // ---- PV: V scale page rows are [other(2r) other(2r+1) scale(r) zp(r)] (8 bytes per key)
+    float s[NB][4][4];
+    // ---- QK: A = codes of keys (g, g+8) of each 16-key group, B = (q' scale_K)^T
 #pragma unroll
     for (int grp = 0; grp < 4; ++grp) {
-        uint32_t a[4];
-        {
-            const uint4 r0 = *reinterpret_cast<const uint4*>(pg + kVScaleOff + (grp * 16 + 2 * t) * 8);      // keys 2t, 2t+1
-            const uint4 r1 = *reinterpret_cast<const uint4*>(pg + kVScaleOff + (grp * 16 + 8 + 2 * t) * 8);  // keys 2t+8, +9
-            const float2 sz00 = unpack_half2(r0.y), sz01 = unpack_half2(r0.w);
-            const float2 sz10 = unpack_half2(r1.y), sz11 = unpack_half2(r1.w);
-            float(&p0)[4] = s[2 * grp], (&p1)[4] = s[2 * grp + 1];
-            acc.z[0] += p0[0] * sz00.y + p0[1] * sz01.y + p1[0] * sz10.y + p1[1] * sz11.y;
-            a[0] = pack_half2(p0[0] * sz00.x, p0[1] * sz01.x);
-            a[2] = pack_half2(p1[0] * sz10.x, p1[1] * sz11.x);
-            if constexpr (kUpper) {
-                acc.z[1] += p0[2] * sz00.y + p0[3] * sz01.y + p1[2] * sz10.y + p1[3] * sz11.y;
-                a[1] = pack_half2(p0[2] * sz00.x, p0[3] * sz01.x);
-                a[3] = pack_half2(p1[2] * sz10.x, p1[3] * sz11.x);
-            } else {
-                a[1] = 0u; a[3] = 0u;
+        const uint4 ka = *reinterpret_cast<const uint4*>(pg + kKCodeOff + (grp * 16 + g) * 64 + 16 * t);
+        const uint4 kb = *reinterpret_cast<const uint4*>(pg + kKCodeOff + (grp * 16 + 8 + g) * 64 + 16 * t);
+        const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb.x, kb.y, kb.z, kb.w};
+        float c[NB][4];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t ua[4], ub[4];
+            unpack8(wa[i], ua);
+            unpack8(wb[i], ub);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                mma16816(c[nb], ua[0], ub[0], ua[1], ub[1], qf.hi[nb][2 * i][0], qf.hi[nb][2 * i][1]);
+                mma16816(c[nb], ua[2], ub[2], ua[3], ub[3], qf.hi[nb][2 * i + 1][0], qf.hi[nb][2 * i + 1][1]);
+                mma16816(c[nb], ua[0], ub[0], ua[1], ub[1], qf.lo[nb][2 * i][0], qf.lo[nb][2 * i][1]);
+                mma16816(c[nb], ua[2], ub[2], ua[3], ub[3], qf.lo[nb][2 * i + 1][0], qf.lo[nb][2 * i + 1][1]);
             }
         }
-        // lane (g, t): 16 dims 16g.. of keys 2t, 2t+1 (b0) and 2t+8, 2t+9 (b1)
+        float o0 = 1.0f, o1 = 1.0f;  // other_K of keys g and g+8 of the group
+        if constexpr (kOther) {
+            o0 = __half2float(*reinterpret_cast<const __half*>(scratch + 512 + (grp * 16 + g) * 2));
+            o1 = __half2float(*reinterpret_cast<const __half*>(scratch + 512 + (grp * 16 + 8 + g) * 2));
+        }
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            s[nb][grp][0] = (c[nb][0] + qf.qz[nb][0]) * o0; s[nb][grp][1] = (c[nb][1] + qf.qz[nb][1]) * o0;
+            s[nb][grp][2] = (c[nb][2] + qf.qz[nb][0]) * o1; s[nb][grp][3] = (c[nb][3] + qf.qz[nb][1]) * o1;
+        }
+    }
+    if (need_mask) {
+#pragma unroll
+        for (int grp = 0; grp < 4; ++grp) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int p = first_pos + grp * 16 + g + (e >> 1) * 8;
+                const bool out = p < key_begin || p >= key_end;
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+                    if (out || p > row_lim[nb][e & 1]) s[nb][grp][e] = -INFINITY;
+            }
+        }
+    }
+    softmax_block<NB, 4>(s, acc);
+    // ---- PV: A = V codes^T (dims x keys), B = (p scale_V)^T.  V scale page rows: [other other scale zp] per key
+#pragma unroll
+    for (int grp = 0; grp < 4; ++grp) {
+        const float2 sz0 = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + kVScaleOff + (grp * 16 + g) * 8 + 4));
+        const float2 sz1 = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + kVScaleOff + (grp * 16 + 8 + g) * 8 + 4));
+        uint32_t b0[NB], b1[NB];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            const float(&p)[4] = s[nb][grp];
+            acc.z[nb][0] += p[0] * sz0.y + p[2] * sz1.y;
+            acc.z[nb][1] += p[1] * sz0.y + p[3] * sz1.y;
+            b0[nb] = movmatrix_trans(pack_half2(p[0] * sz0.x, p[1] * sz0.x));  // -> (row g; keys 2t, 2t+1)
+            b1[nb] = movmatrix_trans(pack_half2(p[2] * sz1.x, p[3] * sz1.x));  // -> (row g; keys 2t+8, 2t+9)
+        }
+        // lane (g, t): 16 dims 16g.. of keys 2t, 2t+1 (pa) and 2t+8, 2t+9 (pb), one half2 per dim
         const uint8_t* vb = pg + kVCodeOff + (grp * 16 + 2 * t) * 64 + 8 * g;
         const uint2 vA = *reinterpret_cast<const uint2*>(vb), vB = *reinterpret_cast<const uint2*>(vb + 64);
         const uint2 vC = *reinterpret_cast<const uint2*>(vb + 512), vD = *reinterpret_cast<const uint2*>(vb + 576);
         const uint32_t wa[2] = {vA.x, vA.y}, wb[2] = {vB.x, vB.y}, wc[2] = {vC.x, vC.y}, wd[2] = {vD.x, vD.y};
+        uint32_t pa[16], pb[16];
 #pragma unroll
         for (int wi = 0; wi < 2; ++wi) {
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
-                // four dims 8wi + 4hh + {0..3} of both key pairs: low 16 bits = first key, high 16 bits = second
-                const uint32_t sel = hh ? 0x7632u : 0x5410u;
+                const uint32_t sel = hh ? 0x7632u : 0x5410u;  // low / high 16 bits of both keys' words
                 const uint32_t x0 = prmt(wa[wi], wb[wi], sel), x1 = prmt(wc[wi], wd[wi], sel);
                 const uint32_t y0 = x0 >> 8, y1 = x1 >> 8;
-                uint32_t b0[4], b1[4];
-                b0[0] = hsub2_u32(lop3_and_or(x0, 0x000F000Fu, 0x64006400u), 0x64006400u);
-                b0[1] = hsub2_u32(lop3_and_or(x0, 0x00F000F0u, 0x54005400u), 0x54005400u);
-                b0[2] = hsub2_u32(lop3_and_or(y0, 0x000F000Fu, 0x64006400u), 0x64006400u);
-                b0[3] = hsub2_u32(lop3_and_or(y0, 0x00F000F0u, 0x54005400u), 0x54005400u);
-                b1[0] = hsub2_u32(lop3_and_or(x1, 0x000F000Fu, 0x64006400u), 0x64006400u);
-                b1[1] = hsub2_u32(lop3_and_or(x1, 0x00F000F0u, 0x54005400u), 0x54005400u);
-                b1[2] = hsub2_u32(lop3_and_or(y1, 0x000F000Fu, 0x64006400u), 0x64006400u);
-                b1[3] = hsub2_u32(lop3_and_or(y1, 0x00F000F0u, 0x54005400u), 0x54005400u);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) mma16816(acc.o[8 * wi + 4 * hh + e], a[0], a[1], a[2], a[3], b0[e], b1[e]);
+                const int d = 8 * wi + 4 * hh;
+                pa[d + 0] = hsub2_u32(lop3_and_or(x0, 0x000F000Fu, 0x64006400u), 0x64006400u);
+                pa[d + 1] = hsub2_u32(lop3_and_or(x0, 0x00F000F0u, 0x54005400u), 0x54005400u);
+                pa[d + 2] = hsub2_u32(lop3_and_or(y0, 0x000F000Fu, 0x64006400u), 0x64006400u);
+                pa[d + 3] = hsub2_u32(lop3_and_or(y0, 0x00F000F0u, 0x54005400u), 0x54005400u);
+                pb[d + 0] = hsub2_u32(lop3_and_or(x1, 0x000F000Fu, 0x64006400u), 0x64006400u);
+                pb[d + 1] = hsub2_u32(lop3_and_or(x1, 0x00F000F0u, 0x54005400u), 0x54005400u);
+                pb[d + 2] = hsub2_u32(lop3_and_or(y1, 0x000F000Fu, 0x64006400u), 0x64006400u);
+                pb[d + 3] = hsub2_u32(lop3_and_or(y1, 0x00F000F0u, 0x54005400u), 0x54005400u);
             }
+        }
+#pragma unroll
+        for (int mb = 0; mb < 8; ++mb) {
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) mma16816(acc.o[nb][mb], pa[mb], pa[8 + mb], pb[mb], pb[8 + mb], b0[nb], b1[nb]);
         }
     }
 }
 
 // 16 keys of the open tile, read un-quantised (fp16, rotated) straight from the stage.
 // krow/vrow point at the first of the 16 stage rows of this head (row stride D halves).
-template <bool kUpper>
-__device__ __forceinline__ void process_stage_group(const __half* krow, const __half* vrow, const QFrag& qf, Acc& acc,
-                                                    int lane, int first_pos, int kv_total, const int (&row_lim)[2],
-                                                    int key_begin, int key_end) {
+template <int NB>
+__device__ __forceinline__ void process_stage_group(const __half* krow, const __half* vrow, const QFrag<NB>& qf,
+                                                    Acc<NB>& acc, int lane, int first_pos, int kv_total,
+                                                    const int (&row_lim)[NB][2], int key_begin, int key_end) {
     const int g = lane >> 2, t = lane & 3;
-    float s[8][4];
+    float s[NB][1][4];
+    {
+        const __half* ka = krow + g * D + 32 * t;
+        const __half* kb = krow + (8 + g) * D + 32 * t;
+        float c[NB][4];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = -INFINITY;
-#pragma unroll
-    for (int nb = 0; nb < 2; ++nb) {
-        const __half* kr = krow + (nb * 8 + g) * D + 32 * t;
-        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int nb = 0; nb < NB; ++nb) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.0f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint4 kw = *reinterpret_cast<const uint4*>(kr + 8 * i);
-            mma16816(c, qf.hi[2 * i][0], qf.hi[2 * i][1], qf.hi[2 * i][2], qf.hi[2 * i][3], kw.x, kw.y);
-            mma16816(c, qf.hi[2 * i + 1][0], qf.hi[2 * i + 1][1], qf.hi[2 * i + 1][2], qf.hi[2 * i + 1][3], kw.z, kw.w);
-            mma16816(c, qf.lo[2 * i][0], qf.lo[2 * i][1], qf.lo[2 * i][2], qf.lo[2 * i][3], kw.x, kw.y);
-            mma16816(c, qf.lo[2 * i + 1][0], qf.lo[2 * i + 1][1], qf.lo[2 * i + 1][2], qf.lo[2 * i + 1][3], kw.z, kw.w);
+            const uint4 a = *reinterpret_cast<const uint4*>(ka + 8 * i), b = *reinterpret_cast<const uint4*>(kb + 8 * i);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                mma16816(c[nb], a.x, b.x, a.y, b.y, qf.hi[nb][2 * i][0], qf.hi[nb][2 * i][1]);
+                mma16816(c[nb], a.z, b.z, a.w, b.w, qf.hi[nb][2 * i + 1][0], qf.hi[nb][2 * i + 1][1]);
+                mma16816(c[nb], a.x, b.x, a.y, b.y, qf.lo[nb][2 * i][0], qf.lo[nb][2 * i][1]);
+                mma16816(c[nb], a.z, b.z, a.w, b.w, qf.lo[nb][2 * i + 1][0], qf.lo[nb][2 * i + 1][1]);
+            }
         }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int p = first_pos + nb * 8 + 2 * t + (e & 1);
-            s[nb][e] = (p > row_lim[e >> 1] || p >= kv_total || p < key_begin || p >= key_end) ? -INFINITY : c[e];
+            const int p = first_pos + g + (e >> 1) * 8;
+            const bool out = p >= kv_total || p < key_begin || p >= key_end;
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) s[nb][0][e] = (out || p > row_lim[nb][e & 1]) ? -INFINITY : c[nb][e];
         }
     }
-    softmax_block<kUpper>(s, acc);
-    uint32_t a[4];
-    a[0] = pack_half2(s[0][0], s[0][1]);
-    a[2] = pack_half2(s[1][0], s[1][1]);
-    a[1] = kUpper ? pack_half2(s[0][2], s[0][3]) : 0u;
-    a[3] = kUpper ? pack_half2(s[1][2], s[1][3]) : 0u;
+    softmax_block<NB, 1>(s, acc);
+    uint32_t b0[NB], b1[NB];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        b0[nb] = movmatrix_trans(pack_half2(s[nb][0][0], s[nb][0][1]));
+        b1[nb] = movmatrix_trans(pack_half2(s[nb][0][2], s[nb][0][3]));
+    }
     // keys at or beyond kv_total hold stale rows: their p is exactly 0; zero V there so 0 * inf cannot appear
     const __half* vb = vrow + (2 * t) * D + 16 * g;
     uint4 v[4][2];
@@ -319,6 +337,7 @@ __device__ __forceinline__ void process_stage_group(const __half* krow, const __
         v[kk][0] = live ? src[0] : make_uint4(0, 0, 0, 0);
         v[kk][1] = live ? src[1] : make_uint4(0, 0, 0, 0);
     }
+    uint32_t pa[16], pb[16];
 #pragma unroll
     for (int h8 = 0; h8 < 2; ++h8) {
         const uint32_t wa[4] = {v[0][h8].x, v[0][h8].y, v[0][h8].z, v[0][h8].w};
@@ -326,15 +345,19 @@ __device__ __forceinline__ void process_stage_group(const __half* krow, const __
         const uint32_t wc[4] = {v[2][h8].x, v[2][h8].y, v[2][h8].z, v[2][h8].w};
         const uint32_t wd[4] = {v[3][h8].x, v[3][h8].y, v[3][h8].z, v[3][h8].w};
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            // register r holds dims 8 h8 + 2r, +1 of one key; pair them across keys (2t, 2t+1) and (2t+8, 2t+9)
-            mma16816(acc.o[8 * h8 + 2 * r], a[0], a[1], a[2], a[3], prmt(wa[r], wb[r], 0x5410), prmt(wc[r], wd[r], 0x5410));
-            mma16816(acc.o[8 * h8 + 2 * r + 1], a[0], a[1], a[2], a[3], prmt(wa[r], wb[r], 0x7632), prmt(wc[r], wd[r], 0x7632));
+        for (int r = 0; r < 4; ++r) {  // register r holds dims 8 h8 + 2r, +1 of one key
+            pa[8 * h8 + 2 * r] = prmt(wa[r], wb[r], 0x5410); pa[8 * h8 + 2 * r + 1] = prmt(wa[r], wb[r], 0x7632);
+            pb[8 * h8 + 2 * r] = prmt(wc[r], wd[r], 0x5410); pb[8 * h8 + 2 * r + 1] = prmt(wc[r], wd[r], 0x7632);
         }
+    }
+#pragma unroll
+    for (int mb = 0; mb < 8; ++mb) {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) mma16816(acc.o[nb][mb], pa[mb], pa[8 + mb], pb[mb], pb[8 + mb], b0[nb], b1[nb]);
     }
 }
 
-template <bool kUpper, bool kOther>
+template <int NB, bool kOther>
 __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(smem_raw);
@@ -346,8 +369,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
     const int key_end = min(P.key_end, kv_total), key_begin = max(P.key_begin, 0);
     const int sealed_pages = 2 * (kv_total / kTile);
 
-    // ---- q' = H q * scale * log2(e) for the 16 rows of this block, stored in fragment order
-    for (int r = warp; r < kRows; r += kWarps) {
+    // ---- q' = H q * scale * log2(e) for the rows of this block, stored in fragment order
+    for (int r = warp; r < 8 * NB; r += kWarps) {
         const int R = zb * kRows + r, tq = R / G, gq = R % G;
         float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         int rp = -1;
@@ -375,18 +398,26 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
     }
     __syncthreads();
 
-    const int g = lane >> 2;
-    int row_lim[2] = {sm.row_pos[g], sm.row_pos[g + 8]};
+    const int g = lane >> 2, t = lane & 3;
+    int row_lim[NB][2];
     int min_lim = INT_MAX;
-    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        row_lim[nb][0] = sm.row_pos[8 * nb + 2 * t];
+        row_lim[nb][1] = sm.row_pos[8 * nb + 2 * t + 1];
+    }
+    for (int r = 0; r < 8 * NB; ++r)
         if (sm.row_pos[r] >= 0) min_lim = min(min_lim, sm.row_pos[r]);
 
-    Acc acc;
+    Acc<NB> acc;
 #pragma unroll
-    for (int n = 0; n < 16; ++n) acc.o[n][0] = acc.o[n][1] = acc.o[n][2] = acc.o[n][3] = 0.0f;
-    acc.m[0] = acc.m[1] = -INFINITY;
-    acc.l[0] = acc.l[1] = acc.z[0] = acc.z[1] = 0.0f;
-    QFrag qf;
+    for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int mb = 0; mb < 8; ++mb) acc.o[nb][mb][0] = acc.o[nb][mb][1] = acc.o[nb][mb][2] = acc.o[nb][mb][3] = 0.0f;
+        acc.m[nb][0] = acc.m[nb][1] = -INFINITY;
+        acc.l[nb][0] = acc.l[nb][1] = acc.z[nb][0] = acc.z[nb][1] = 0.0f;
+    }
+    QFrag<NB> qf;
     bool timed_out = false;
 
     if (split < P.nsplit) {
@@ -429,7 +460,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
                     __syncwarp();
                     transpose_k_scale(pg + kKScaleOff, scratch, lane);
                     __syncwarp();
-                    build_qfrag<true>(sm, scratch, lane, qf);
+                    build_qfrag<true, NB>(sm, scratch, lane, qf);
                 } else if constexpr (kOther) {
                     __syncwarp();
                     transpose_k_scale(pg + kKScaleOff, scratch, lane);
@@ -437,7 +468,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
                 }
                 const int first = lp * kPage;
                 const bool need_mask = first + kPage - 1 > min_lim || first < key_begin || first + kPage > key_end;
-                process_page<kUpper, kOther>(pg, scratch, qf, acc, lane, need_mask, first, row_lim, key_begin, key_end);
+                process_page<NB, kOther>(pg, scratch, qf, acc, lane, need_mask, first, row_lim, key_begin, key_end);
             }
             // refill this slot with the page after next; the generic-proxy reads above must be ordered first
             __syncwarp();
@@ -460,41 +491,45 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
         const int tile = kv_total / kTile, base = tile * kTile;
         const int first = base + 16 * warp;
         if (first < key_end && first + 16 > key_begin && first < kv_total) {
-            build_qfrag<false>(sm, nullptr, lane, qf);
-            process_stage_group<kUpper>(L.stage_row(0, tile & 1, head, 16 * warp), L.stage_row(1, tile & 1, head, 16 * warp), qf,
-                                        acc, lane, first, kv_total, row_lim, key_begin, key_end);
+            build_qfrag<false, NB>(sm, nullptr, lane, qf);
+            process_stage_group<NB>(L.stage_row(0, tile & 1, head, 16 * warp), L.stage_row(1, tile & 1, head, 16 * warp), qf,
+                                    acc, lane, first, kv_total, row_lim, key_begin, key_end);
         }
     }
 
     // ---- merge the 8 warps of the CTA (log-sum-exp) and store one partial per row
     __syncthreads();  // every slot has been consumed: the ring memory becomes the merge buffer
-    constexpr int kORow = 4 * 33, kWarpFloats = 3 * kRows + kRows * kORow;
-    float* mb = reinterpret_cast<float*>(sm.slots) + warp * kWarpFloats;
-    const int t = lane & 3;
+    constexpr int kORow = D + 4, kWarpFloats = 3 * kRows + kRows * kORow;
+    float* mbuf = reinterpret_cast<float*>(sm.slots) + warp * kWarpFloats;
 #pragma unroll
-    for (int hf = 0; hf < 2; ++hf) {
-        acc.l[hf] += __shfl_xor_sync(0xffffffffu, acc.l[hf], 1);
-        acc.l[hf] += __shfl_xor_sync(0xffffffffu, acc.l[hf], 2);
-        acc.z[hf] += __shfl_xor_sync(0xffffffffu, acc.z[hf], 1);
-        acc.z[hf] += __shfl_xor_sync(0xffffffffu, acc.z[hf], 2);
-        if (t == 0) {
-            mb[g + 8 * hf] = acc.m[hf];
-            mb[kRows + g + 8 * hf] = acc.l[hf];
-            mb[2 * kRows + g + 8 * hf] = acc.z[hf];
+    for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int o = 4; o <= 16; o <<= 1) {
+                acc.l[nb][j] += __shfl_xor_sync(0xffffffffu, acc.l[nb][j], o);
+                acc.z[nb][j] += __shfl_xor_sync(0xffffffffu, acc.z[nb][j], o);
+            }
+            if (g == 0) {
+                const int row = 8 * nb + 2 * t + j;
+                mbuf[row] = acc.m[nb][j];
+                mbuf[kRows + row] = acc.l[nb][j];
+                mbuf[2 * kRows + row] = acc.z[nb][j];
+            }
         }
-    }
-    float* ob = mb + 3 * kRows;
+        float* ob = mbuf + 3 * kRows + (8 * nb + 2 * t) * kORow + 16 * g;
 #pragma unroll
-    for (int nb = 0; nb < 16; ++nb) {
-        ob[g * kORow + t * 33 + nb] = acc.o[nb][0];
-        ob[g * kORow + t * 33 + 16 + nb] = acc.o[nb][1];
-        ob[(g + 8) * kORow + t * 33 + nb] = acc.o[nb][2];
-        ob[(g + 8) * kORow + t * 33 + 16 + nb] = acc.o[nb][3];
+        for (int mb = 0; mb < 8; ++mb) {
+            ob[mb] = acc.o[nb][mb][0];
+            ob[kORow + mb] = acc.o[nb][mb][1];
+            ob[8 + mb] = acc.o[nb][mb][2];
+            ob[kORow + 8 + mb] = acc.o[nb][mb][3];
+        }
     }
     __syncthreads();
     const float* all = reinterpret_cast<const float*>(sm.slots);
     const int64_t pidx = ((static_cast<int64_t>(head) * gridDim.z + zb) * (P.nsplit + 1) + split) * kRows;
-    for (int e = threadIdx.x; e < kRows * D; e += kThreads) {
+    for (int e = threadIdx.x; e < 8 * NB * D; e += kThreads) {
         const int row = e / D, d = e % D;
         float m = -INFINITY;
 #pragma unroll
@@ -506,7 +541,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
                 const float* wb = all + w * kWarpFloats;
                 const float wt = fast_exp2(wb[row] - m);  // exp2(-inf) = 0 for a warp that saw no key
                 l += wt * wb[kRows + row];
-                o += wt * (wb[3 * kRows + row * kORow + (d >> 5) * 33 + (d & 31)] + wb[2 * kRows + row]);
+                o += wt * (wb[3 * kRows + row * kORow + d] + wb[2 * kRows + row]);
             }
         }
         P.ws_o[(pidx + row) * D + d] = o;
@@ -516,38 +551,72 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
 
 // Merge the partials of all splits of one query row, normalise, rotate back (H is its own inverse) and
 // store in the output dtype -- or, for a sharded decode, export the merged partial (m in natural-log
-// units, l, o in the rotated domain).  One warp per (token, q head).
-__global__ void __launch_bounds__(128) reduce_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
-                                                     const float* __restrict__ ws_o, int parts, int T, int q_heads,
-                                                     int kv_heads, int zblocks, int dtype, uint16_t* __restrict__ out,
-                                                     float* __restrict__ part_m, float* __restrict__ part_l,
-                                                     float* __restrict__ part_o) {
-    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= T * q_heads) return;
+// units, l, o in the rotated domain).  One CTA of 8 warps per (token, q head): warp w takes parts
+// w, w+8, ... and issues all its loads before using any (the kernel is pure load latency), lane l owns
+// dims 4l..4l+3; the eight warp sums meet in shared memory and warp 0 finishes the row.
+constexpr int kReduceWarps = 8, kMaxPartsPerWarp = 8;  // up to 64 parts
+__global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
+                                                                  const float* __restrict__ ws_o, int parts, int T, int q_heads,
+                                                                  int kv_heads, int zblocks, int dtype, uint16_t* __restrict__ out,
+                                                                  float* __restrict__ part_m, float* __restrict__ part_l,
+                                                                  float* __restrict__ part_o) {
+    __shared__ float4 so[kReduceWarps][32];
+    __shared__ float sl[kReduceWarps];
+    const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = q_heads / kv_heads, tq = row / q_heads, qh = row % q_heads, head = qh / G, gq = qh % G;
     const int R = tq * G + gq, zb = R / kRows, r = R % kRows;
     const int64_t base = (static_cast<int64_t>(head) * zblocks + zb) * parts * kRows + r;
-    float m = -INFINITY;
-    for (int p = 0; p < parts; ++p) m = fmaxf(m, ws_m[base + static_cast<int64_t>(p) * kRows]);
-    float l = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    if (m != -INFINITY) {
-        for (int p = 0; p < parts; ++p) {
-            const int64_t i = base + static_cast<int64_t>(p) * kRows;
-            const float w = fast_exp2(ws_m[i] - m);
-            l += w * ws_l[i];
+    // every warp finds the global maximum (parts <= 64: two loads per lane)
+    float m = lane < parts ? ws_m[base + static_cast<int64_t>(lane) * kRows] : -INFINITY;
+    if (lane + 32 < parts) m = fmaxf(m, ws_m[base + static_cast<int64_t>(lane + 32) * kRows]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o[j] += w * ws_o[i * D + lane + 32 * j];
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float4 v[kMaxPartsPerWarp];
+    float pm[kMaxPartsPerWarp], pl[kMaxPartsPerWarp];
+#pragma unroll
+    for (int i = 0; i < kMaxPartsPerWarp; ++i) {
+        const int p = warp + kReduceWarps * i;
+        const bool on = p < parts;
+        const int64_t idx = base + static_cast<int64_t>(on ? p : 0) * kRows;
+        pm[i] = on ? ws_m[idx] : -INFINITY;
+        pl[i] = on ? ws_l[idx] : 0.0f;
+        v[i] = on ? *reinterpret_cast<const float4*>(ws_o + idx * D + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l = 0.0f;
+    if (m != -INFINITY) {
+#pragma unroll
+        for (int i = 0; i < kMaxPartsPerWarp; ++i) {
+            const float w = fast_exp2(pm[i] - m);
+            l += w * pl[i];
+            acc.x += w * v[i].x; acc.y += w * v[i].y; acc.z += w * v[i].z; acc.w += w * v[i].w;
         }
+    }
+    so[warp][lane] = acc;
+    if (lane == 0) sl[warp] = l;
+    __syncthreads();
+    if (warp != 0) return;
+    acc = so[0][lane];
+    l = sl[0];
+#pragma unroll
+    for (int w = 1; w < kReduceWarps; ++w) {
+        const float4 x = so[w][lane];
+        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+        l += sl[w];
     }
     if (part_m != nullptr) {
         if (lane == 0) { part_m[row] = m * kLn2; part_l[row] = l; }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) part_o[static_cast<int64_t>(row) * D + lane + 32 * j] = o[j];
+        *reinterpret_cast<float4*>(part_o + static_cast<int64_t>(row) * D + 4 * lane) = acc;
         return;
     }
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    // the rotation wants lane l to hold dims l + 32 j: re-distribute through shared memory
+    so[0][lane] = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    __syncwarp();
+    const float* flat = reinterpret_cast<const float*>(so[0]);
+    float o[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o[j] *= inv;
+    for (int j = 0; j < 4; ++j) o[j] = flat[lane + 32 * j];
     hadamard_warp<D>(o, lane);
 #pragma unroll
     for (int j = 0; j < 4; ++j)
@@ -603,6 +672,7 @@ int split_count(int kv_len_max, int kv_heads, int zblocks) {
     n = n < 1 ? 1 : n;
     const int by_pages = (pages + 1) / 2;  // at least two pages per CTA
     if (n > by_pages) n = by_pages;
+    if (n > kReduceWarps * kMaxPartsPerWarp - 1) n = kReduceWarps * kMaxPartsPerWarp - 1;  // reduce_kernel holds 64 parts
     return n < 1 ? 1 : n;
 }
 
@@ -646,16 +716,16 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     const int smem = static_cast<int>(sizeof(AttnSmem));
     static bool opted = false;
     if (!opted) {
-        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         opted = true;
     }
     const dim3 grid(parts, layer->kv_heads, Z);
-    if (upper) attn_kernel<true, false><<<grid, kThreads, smem, stream>>>(P);
-    else attn_kernel<false, false><<<grid, kThreads, smem, stream>>>(P);
+    if (upper) attn_kernel<2, false><<<grid, kThreads, smem, stream>>>(P);
+    else attn_kernel<1, false><<<grid, kThreads, smem, stream>>>(P);
     KVB_CUDA_OK(cudaGetLastError());
     const int total_rows = T * layer->q_heads;
-    reduce_kernel<<<(total_rows + 3) / 4, 128, 0, stream>>>(P.ws_m, P.ws_l, P.ws_o, parts, T, layer->q_heads, layer->kv_heads, Z,
+    reduce_kernel<<<total_rows, kReduceWarps * 32, 0, stream>>>(P.ws_m, P.ws_l, P.ws_o, parts, T, layer->q_heads, layer->kv_heads, Z,
                                                             layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o);
     KVB_CUDA_OK(cudaGetLastError());
     return KVB_OK;
