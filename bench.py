@@ -25,6 +25,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 D, H, QH, LAYERS, CTX = 128, 4, 24, 16, 32768
+TRAFFIC_BYTES_PER_TOKEN = 596.7
 SEALED_B, TAIL_B = 140, 512  # algorithmic bytes per sealed / open-tile token per KV head (codes + 12 B of axes | fp16 K+V rows)
 
 
@@ -306,9 +307,9 @@ def run_gpu(args):
             "parity": {"max_abs_over_ref_max": err, "checked": f"layer 0 decode at {cur} tokens vs CPU oracle"},
             "clocks": clocks,
         }
-        tr = os.path.join(ROOT, "profiles", "attn_kernel_traffic.json")
-        if os.path.exists(tr):
-            result["roofline"]["traffic"] = json.load(open(tr)).get("dram_bytes_per_launch_at_bench_size")
+        # DRAM bytes per launch: one ncu capture at 131,072 tokens (profiles/attn_kernel_decode_ctx131072.md),
+        # 596.7 B per token of context, scaled to this context (traffic grows in proportion to it)
+        result["roofline"]["traffic"] = TRAFFIC_BYTES_PER_TOKEN * (CTX + 1)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

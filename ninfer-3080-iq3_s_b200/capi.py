@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libkvarn_b200.so")
+LIB_PATH = os.environ.get("KVB_LIBRARY", os.path.join(_HERE, "libkvarn_b200.so"))
 
 KVB_OK, KVB_EINVAL, KVB_ECUDA, KVB_ERANGE, KVB_ETIMEOUT = range(5)
 DTYPE_F16, DTYPE_BF16 = 0, 1
