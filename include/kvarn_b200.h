@@ -9,8 +9,7 @@
  * Conventions
  *   - plain pointers and sizes; every buffer is caller-owned DEVICE memory unless stated.
  *   - `stream` is a cudaStream_t passed as void*.
- *   - calls are asynchronous on `stream`; none synchronises, none allocates (except the
- *     one-time set-up noted at kvb_attn_decode_static).
+ *   - calls are asynchronous on `stream`; none synchronises, none allocates.
  *   - no exceptions cross the ABI: functions return a kvb_status; kvb_last_error_string()
  *     gives the text of the calling thread's last failure.
  *   - positions and block tables are read on the device only (the reference's hard rule,
@@ -106,6 +105,20 @@ size_t kvb_workspace_bytes(int kv_len_max, int kv_heads, int q_heads, int head_d
  * Replaces causal_attention_cached_small_t_launch (P3:3612-3696). */
 int kvb_attn_decode(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
                     void* workspace, void* out, void* stream);
+
+/* Decode attention without a caller-supplied workspace.  No counterpart in the reference.
+ * For hosts that cannot get device memory while they run -- an engine whose KV pool took the whole GPU at
+ * start-up, a serving thread that must stay away from the allocator -- the split-K partials live in a fixed
+ * 2 MiB array inside the library (kvb_static_scratch_bytes()); every GPU that loads the library holds it until
+ * the process exits.  Same arguments and result as kvb_attn_decode minus the workspace.  The call allocates
+ * nothing.  The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ * device current); make that first call before any stream capture begins.  Shapes whose partials do not fit
+ * (kvb_workspace_bytes(...) > kvb_static_scratch_bytes()) are refused with KVB_ERANGE.  All calls on a device
+ * share the one array, which keeps what the previous call left in it -- nothing in it needs clearing, each call
+ * writes every entry before reading it -- so two calls that overlap on the GPU (different streams) race. */
+size_t kvb_static_scratch_bytes(void);
+int kvb_attn_decode_static(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
+                           void* out, void* stream);
 
 /* Same, but stops before the final normalisation: writes the log-sum-exp partial of keys
  * [key_begin, key_end) -- part_m[q_heads] (max logit, natural log units), part_l[q_heads] (sum of

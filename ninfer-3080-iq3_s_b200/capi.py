@@ -44,6 +44,8 @@ SYMBOLS = {
     "kvb_workspace_bytes": (C.c_size_t, [C.c_int] * 6),
     "kvb_attn_decode": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p,
                                   C.c_void_p, C.c_void_p]),
+    "kvb_static_scratch_bytes": (C.c_size_t, []),
+    "kvb_attn_decode_static": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p, C.c_void_p]),
     "kvb_attn_decode_partial": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int,
                                           C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "kvb_merge_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,

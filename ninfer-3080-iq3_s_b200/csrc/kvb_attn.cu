@@ -807,3 +807,60 @@ extern "C" int kvb_attn_prefill(const kvb_layer* layer, const void* q, const voi
     }
     return KVB_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot provide a workspace.
+//
+// Some hosts of this library have no way to obtain device memory once they are running: an inference engine
+// that sized its KV pool to fill the GPU at start-up has nothing left to allocate from, and a serving thread
+// may be forbidden to touch the allocator at all.  For them the split-K partials of kvb_attn_decode live in
+// the fixed array below instead of a caller-supplied buffer.  The array is part of the library image: every
+// GPU that loads the library holds these 2 MiB until the process exits, whether or not the entry point is
+// ever called.
+//
+// `g_static_scratch` is a device symbol.  In host code its name is only a stand-in and must never be handed
+// to a kernel; the device address is obtained once per device with cudaGetSymbolAddress (below) and that
+// pointer is what the kernels receive.
+constexpr size_t kStaticScratchBytes = 2u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace kvb {
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};  // device address of g_static_scratch, per device ordinal
+
+// First use on the current device: look the symbol up (no allocation happens here or anywhere below).
+int static_scratch_for_current_device(void** out) {
+    int dev = -1;
+    KVB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(KVB_ERANGE, "kvb_attn_decode_static: device ordinal %d (0..%d supported)", dev, kMaxDevices - 1);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        KVB_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (p == nullptr) return fail(KVB_ECUDA, "kvb_attn_decode_static: cudaGetSymbolAddress returned a null address");
+        g_static_scratch_ptr[dev] = p;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return KVB_OK;
+}
+}  // namespace
+}  // namespace kvb
+
+extern "C" size_t kvb_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int kvb_attn_decode_static(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
+                                      void* out, void* stream) {
+    using namespace kvb;
+    if (int st = check_layer(layer, "kvb_attn_decode_static")) return st;
+    const size_t need = kvb_workspace_bytes(kv_len_max, layer->kv_heads, layer->q_heads, layer->head_dim, 1, 1);
+    if (need == 0 || need > kStaticScratchBytes)
+        return fail(KVB_ERANGE,
+                    "kvb_attn_decode_static: this shape needs %zu bytes of split-K scratch, the built-in array holds %zu; "
+                    "use kvb_attn_decode with a caller-owned workspace",
+                    need, kStaticScratchBytes);
+    void* scratch = nullptr;
+    if (int st = static_scratch_for_current_device(&scratch)) return st;
+    // Nothing in the scratch has to start at zero: every partial the merge reads is written earlier in the same call.
+    return launch_attention(layer, q, pos_dev, pos_dev, 1, scale, kv_len_max, 0, INT_MAX, scratch, out, nullptr, nullptr, nullptr,
+                            static_cast<cudaStream_t>(stream), "kvb_attn_decode_static");
+}
