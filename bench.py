@@ -317,17 +317,297 @@ def run_gpu(args):
         print(json.dumps(result))
 
 
+# ------------------------------------------------------------------------------------------------------------
+# Other workloads of BASELINE.json (not the contract line): selected with --workload.
+# ------------------------------------------------------------------------------------------------------------
+class _Env:
+    """Device, process group and helpers shared by the extra workloads."""
+
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+
+        import __graft_entry__ as entry
+
+        self.torch, self.dist = torch, dist
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.pkg = entry.load_package()
+        self.pkg.capi.load()
+        self.gen = torch.Generator(device=self.dev)
+        self.gen.manual_seed(7 + 1000 * self.rank)
+        self.scale = 1.0 / math.sqrt(D)
+
+    def synth(self, tokens, heads):
+        x = self.torch.randn((tokens, heads, D), generator=self.gen, device=self.dev, dtype=self.torch.float32)
+        x[..., [3, 17, 64, 101]] *= 20.0
+        return x.to(self.torch.float16)
+
+    def layer(self, tokens, room, seed):
+        """A layer pre-filled with `tokens` synthetic tokens and room for `room` more."""
+        from oracle import kvarn_oracle as orc
+
+        torch = self.torch
+        lp = (tokens + room + 63) // 64 + 2
+        lp += lp & 1
+        L = self.pkg.KvarnLayer(D, H, QH, lp, torch.from_numpy(orc.shuffled_table(seed, lp, lp)), device=str(self.dev))
+        for c0 in range(0, tokens, 8192):
+            n = min(8192, tokens - c0)
+            L.append(self.synth(n, H), self.synth(n, H), torch.arange(c0, c0 + n, dtype=torch.int32, device=self.dev))
+        return L
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def timed(self, fn, n):
+        torch = self.torch
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        self.barrier()
+        ms = e0.elapsed_time(e1)
+        if self.world > 1:
+            t = torch.tensor([ms], device=self.dev)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / n
+
+    def graph(self, body):
+        """Capture `body` into a CUDA graph (after one eager run); falls back to eager replay if capture fails."""
+        torch = self.torch
+        body()
+        torch.cuda.synchronize()
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=torch.cuda.Stream(device=self.dev)):
+                body()
+            torch.cuda.synchronize()
+            return g.replay, True
+        except Exception:  # noqa: BLE001 -- e.g. a collective that cannot be captured on this stack
+            torch.cuda.synchronize()
+            return body, False
+
+    def finish(self, result):
+        if self.world > 1:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+        if self.rank == 0:
+            print(json.dumps(result))
+
+
+def run_long(args):
+    """BASELINE config 4A: one 378,944-token sequence, batch-1 decode, range-sharded over the ranks; per layer each
+    rank attends its tile range, one all-gather of (m, l, o) partials, every rank merges."""
+    E = _Env()
+    torch = E.torch
+    sh = E.pkg.sharded
+    ctx, layers_n = 378944, args.layers or 4
+    b, e = sh.tile_ranges(ctx, E.world)[E.rank]
+    n = e - b
+    layers = [E.layer(n, 8, 100 * E.rank + i) for i in range(layers_n)]
+    q = torch.randn((layers_n, QH, D), generator=E.gen, device=E.dev).to(torch.float16)
+    if E.world > 1:
+        E.dist.broadcast(q, 0)
+    pos = torch.full((1,), n - 1, dtype=torch.int32, device=E.dev)
+    outs = torch.empty((layers_n, QH, D), dtype=torch.float16, device=E.dev)
+    for L in layers:
+        L.workspace(n + 8, 1)
+    dec = [sh.ShardedDecode(L) for L in layers]
+
+    def step():
+        for i, L in enumerate(layers):
+            if E.world == 1:
+                L.attn_decode(q[i], pos, E.scale, n + 8, out=outs[i])
+            else:
+                outs[i].copy_(dec[i].attn_decode(q[i], pos, E.scale, n + 8))
+
+    def step_local():  # the same without the collective: partial + merge of the rank's own partial
+        for i, L in enumerate(layers):
+            m, l, o = L.attn_decode_partial(q[i], pos, E.scale, n + 8)
+            outs[i].copy_(E.pkg.merge_partials(m.unsqueeze(0), l.unsqueeze(0), o.unsqueeze(0)))
+
+    run, graphed = E.graph(step)
+    with ClockSampler(E.local) as clk:
+        for _ in range(max(args.warmup, 3)):
+            run()
+        ms = E.timed(run, args.steps)
+        run_l, _ = E.graph(step_local)
+        for _ in range(3):
+            run_l()
+        ms_local = E.timed(run_l, args.steps)
+    peak, kind = peaks()
+    nbytes = decode_bytes(ctx)
+    us_layer = ms * 1e3 / layers_n
+    E.finish({
+        "metric": "decode_attn_hbm_gbs", "value": nbytes / (us_layer * 1e-6) / 1e9, "unit": "GB/s", "n_gpus": E.world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "us_per_layer": us_layer,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "decode_ctx378944_b1 (BASELINE config 4A), context range-sharded by tiles", "layers": layers_n,
+                   "ctx": ctx, "q_heads": QH, "kv_heads": H, "head_dim": D, "parallelism": f"sp{E.world} (tile ranges + NCCL all-gather of partials)",
+                   "l2": f"{layers_n} layers x {n * H * 146 / 1e6:.0f} MB per rank between revisits"},
+        "pct_of_hbm_peak": 100.0 * nbytes / (us_layer * 1e-6) / 1e9 / (peak * E.world), "peak_kind": kind,
+        "combine": {"us_per_layer_with_gather": us_layer, "us_per_layer_partial_and_merge_only": ms_local * 1e3 / layers_n,
+                    "share_of_layer_time": max(0.0, 1.0 - ms_local / ms) if E.world > 1 else 0.0, "graph_captured": graphed,
+                    "bytes_per_rank_per_layer": QH * (D + 2) * 4},
+        "clocks": clk.summary(), "gpu_launches": args.steps * layers_n * (2 if E.world == 1 else 3),
+    })
+
+
+def run_batch(args):
+    """BASELINE config 4B: 32 independent sequences, lengths seed-uniform in 16K..131K, sharded by sequence; one
+    layer per sequence, a step = one decode call per local sequence."""
+    import random
+
+    E = _Env()
+    torch = E.torch
+    rnd = random.Random(0)
+    lengths = [rnd.randint(16384, 131072) for _ in range(32)]
+    mine = E.pkg.sharded.deal_sequences(lengths, E.world)[E.rank]
+    seqs = [(E.layer(lengths[i], 8, i), lengths[i]) for i in mine]
+    q = torch.randn((len(seqs), QH, D), generator=E.gen, device=E.dev).to(torch.float16)
+    poss = [torch.full((1,), n - 1, dtype=torch.int32, device=E.dev) for _, n in seqs]
+    outs = torch.empty((len(seqs), QH, D), dtype=torch.float16, device=E.dev)
+    for L, n in seqs:
+        L.workspace(n + 8, 1)
+
+    def step():
+        for i, (L, n) in enumerate(seqs):
+            L.attn_decode(q[i], poss[i], E.scale, n + 8, out=outs[i])
+
+    run, graphed = E.graph(step)
+    with ClockSampler(E.local) as clk:
+        for _ in range(max(args.warmup, 3)):
+            run()
+        ms = E.timed(run, args.steps)
+    peak, kind = peaks()
+    total = sum(decode_bytes(n) for n in lengths)
+    E.finish({
+        "metric": "decode_attn_hbm_gbs", "value": total / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": E.world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "decode_batch32_len16k-131k (BASELINE config 4B), sharded by sequence", "sequences": 32,
+                   "total_tokens": sum(lengths), "q_heads": QH, "kv_heads": H, "head_dim": D, "parallelism": f"dp{E.world} (LPT by length, no collective)",
+                   "l2": f"{total / 1e9:.2f} GB of KV per step"},
+        "pct_of_hbm_peak": 100.0 * total / (ms * 1e-3) / 1e9 / (peak * E.world), "peak_kind": kind, "graph_captured": graphed,
+        "clocks": clk.summary(), "gpu_launches": args.steps * len(seqs) * 2,
+    })
+
+
+def run_verify(args):
+    """BASELINE config 2: MTP draft-verify at 131,072 tokens: append 1+k rows (k seeded in 3..7), causal attention of
+    those rows; the drafts are rolled back after every step, so the context stays at 131,072."""
+    import random
+
+    E = _Env()
+    torch = E.torch
+    ctx, layers_n = 131072, args.layers or 4
+    layers = [E.layer(ctx, 16, i) for i in range(layers_n)]
+    rnd = random.Random(0)
+    widths = [1 + rnd.randint(3, 7) for _ in range(16)]
+    q = torch.randn((layers_n, 8, QH, D), generator=E.gen, device=E.dev).to(torch.float16)
+    kv = [E.synth(8, 2 * H) for _ in range(layers_n)]
+    pos = torch.arange(ctx, ctx + 8, dtype=torch.int32, device=E.dev)
+    outs = torch.empty((layers_n, 8, QH, D), dtype=torch.float16, device=E.dev)
+    for L in layers:
+        L.workspace(ctx + 16, 8)
+    runs = {}
+    for w in sorted(set(widths)):
+        def body(w=w):
+            for i, L in enumerate(layers):
+                L.attn_verify(q[i, :w], kv[i][:w, :H], kv[i][:w, H:], pos[:w], E.scale, ctx + 16, out=outs[i, :w])
+        runs[w] = E.graph(body)[0]
+    seq = [runs[w] for w in widths]
+    it = {"i": 0}
+
+    def step():
+        seq[it["i"] % len(seq)]()
+        it["i"] += 1
+
+    with ClockSampler(E.local) as clk:
+        for _ in range(max(args.warmup, 3)):
+            step()
+        it["i"] = 0
+        ms = E.timed(step, args.steps)
+    peak, kind = peaks()
+    used = [widths[i % len(widths)] for i in range(args.steps)]
+    nbytes = decode_bytes(ctx)
+    flops = sum(4.0 * QH * w * ctx * D for w in used) / len(used)
+    us_layer = ms * 1e3 / layers_n
+    E.finish({
+        "metric": "verify_attn_hbm_gbs", "value": nbytes / (us_layer * 1e-6) / 1e9, "unit": "GB/s", "n_gpus": E.world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "us_per_layer": us_layer, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "mtp_verify_ctx131072 (BASELINE config 2)", "layers": layers_n, "widths": used[:16], "q_heads": QH,
+                   "kv_heads": H, "head_dim": D, "l2": f"{layers_n} layers x 77 MB between revisits"},
+        "pct_of_hbm_peak": 100.0 * nbytes / (us_layer * 1e-6) / 1e9 / peak, "peak_kind": kind,
+        "tflops": flops / (us_layer * 1e-6) / 1e12, "clocks": clk.summary(), "gpu_launches": args.steps * layers_n * 3,
+    })
+
+
+def run_prefill(args):
+    """BASELINE config 3: quantise-append a 1,024-token chunk and run causal chunk attention over a 262,144-token
+    prefix; the chunk is rolled back after every step."""
+    E = _Env()
+    torch = E.torch
+    ctx, chunk = args.ctx or 262144, 1024
+    L = E.layer(ctx, chunk + 8, 0)
+    q = torch.randn((chunk, QH, D), generator=E.gen, device=E.dev).to(torch.float16)
+    k, v = E.synth(chunk, H), E.synth(chunk, H)
+    pos = torch.arange(ctx, ctx + chunk, dtype=torch.int32, device=E.dev)
+    out = torch.empty_like(q)
+
+    def step():
+        L.attn_prefill(q, k, v, pos, E.scale, ctx + chunk + 8, out=out)
+
+    step()
+    with ClockSampler(E.local) as clk:
+        for _ in range(max(args.warmup, 1)):
+            step()
+        ms = E.timed(step, args.steps)
+    flops = 4.0 * QH * D * (chunk * ctx + chunk * (chunk + 1) / 2)
+    tf = flops / (ms * 1e-3) / 1e12
+    peak_tf = 1388.5
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        peak_tf = float(json.load(open(p))["bf16_tflops_sustained"])
+    E.finish({
+        "metric": "prefill_chunk_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": E.world, "steps": args.steps,
+        "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"prefill_chunk1024_prefix{ctx} (BASELINE config 3)", "layers": 1, "q_heads": QH, "kv_heads": H, "head_dim": D},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf, "traffic": None},
+        "clocks": clk.summary(),
+    })
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="decode32k", choices=["decode32k", "long379k", "batch32", "verify131k", "prefill262k"],
+                    help="decode32k is the contract line; the others are BASELINE configs 4A, 4B, 2 and 3")
+    ap.add_argument("--layers", type=int, default=0, help="layers held for long379k / verify131k (default 4)")
+    ap.add_argument("--ctx", type=int, default=0, help="prefix length for prefill262k (default 262144)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
-    else:
+    elif args.workload == "decode32k":
         run_gpu(args)
+    else:
+        {"long379k": run_long, "batch32": run_batch, "verify131k": run_verify, "prefill262k": run_prefill}[args.workload](args)
 
 
 if __name__ == "__main__":

@@ -14,6 +14,10 @@ from .build import build  # noqa: F401
 
 
 def __getattr__(name):
+    if name == "sharded":
+        import importlib
+
+        return importlib.import_module(__name__ + ".sharded")
     if name in ("KvarnLayer", "merge_partials", "default_scale", "cache"):
         import importlib
 

@@ -1,0 +1,80 @@
+"""Multi-GPU use of the path, one process per GPU (torch.distributed, NCCL over NVLink on GPUs, gloo in the
+CPU tests).  The reference is single-GPU (kvarn-port has no collective call site), so this layer is new:
+
+* one long sequence: the context is cut into contiguous tile ranges, one per rank, each rank holding its range
+  as a local cache of its own; every rank attends its range, exports the log-sum-exp partial (m, l, o_rot)
+  per query head, one all-gather moves the partials (q_heads * (head_dim + 2) floats per rank) and every rank
+  merges them.  The open tile lives on the last rank, which also receives the appends.
+* many independent sequences: whole sequences are dealt to ranks, longest first onto the least loaded rank;
+  no communication on the data path.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+TILE = 128
+
+
+def tile_ranges(kv_len: int, world: int) -> List[Tuple[int, int]]:
+    """Token range [begin, end) of every rank: whole tiles, contiguous, as even as possible; the remainder
+    (open tile) goes to the last rank.  Ranks beyond the number of tiles get empty ranges."""
+    tiles = kv_len // TILE
+    per, extra = divmod(tiles, world)
+    out, t = [], 0
+    for r in range(world):
+        n = per + (1 if r < extra else 0)
+        out.append((t * TILE, (t + n) * TILE))
+        t += n
+    b, _ = out[-1]
+    out[-1] = (b, kv_len)
+    return out
+
+
+def deal_sequences(lengths: Sequence[int], world: int) -> List[List[int]]:
+    """Longest-processing-time greedy: indices of the sequences each rank serves."""
+    load = [0] * world
+    owner: List[List[int]] = [[] for _ in range(world)]
+    for i in sorted(range(len(lengths)), key=lambda j: -lengths[j]):
+        r = min(range(world), key=lambda k: (load[k], k))
+        owner[r].append(i)
+        load[r] += lengths[i]
+    return owner
+
+
+def pack_partial(m, l, o):
+    """(m [QH], l [QH], o [QH, D]) -> one [QH, D + 2] tensor for a single all-gather."""
+    import torch
+
+    return torch.cat([m.unsqueeze(1), l.unsqueeze(1), o], dim=1).contiguous()
+
+
+def unpack_partials(buf):
+    """[R, QH, D + 2] -> m [R, QH], l [R, QH], o [R, QH, D] (contiguous copies)."""
+    return buf[..., 0].contiguous(), buf[..., 1].contiguous(), buf[..., 2:].contiguous()
+
+
+def all_gather_partials(packed, group=None):
+    """One collective per layer call: every rank ends with [world, QH, D + 2]."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    out = torch.empty((world * packed.shape[0],) + tuple(packed.shape[1:]), dtype=packed.dtype, device=packed.device)
+    dist.all_gather_into_tensor(out, packed, group=group)  # rank r's block lands at rows [r * QH, (r + 1) * QH)
+    return out.view((world,) + tuple(packed.shape))
+
+
+class ShardedDecode:
+    """Decode attention of one sequence whose cache is range-sharded over the ranks of `group`.
+    `layer` is this rank's local KvarnLayer holding `local_len` tokens (its range, local positions 0..)."""
+
+    def __init__(self, layer, group=None):
+        self.layer, self.group = layer, group
+
+    def attn_decode(self, q, local_pos, scale: float, local_len_max: int, out_dtype=None):
+        from . import cache
+
+        m, l, o = self.layer.attn_decode_partial(q, local_pos, scale, local_len_max)
+        gathered = all_gather_partials(pack_partial(m, l, o), self.group)
+        gm, gl, go = unpack_partials(gathered)
+        return cache.merge_partials(gm, gl, go, dtype=out_dtype or self.layer.dtype)
