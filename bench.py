@@ -423,26 +423,29 @@ def run_long(args):
     outs = torch.empty((layers_n, QH, D), dtype=torch.float16, device=E.dev)
     for L in layers:
         L.workspace(n + 8, 1)
-    dec = [sh.ShardedDecode(L) for L in layers]
+    dec = [sh.ShardedDecode(L) for L in layers] if E.world > 1 else []
 
     def step():
         for i, L in enumerate(layers):
             if E.world == 1:
                 L.attn_decode(q[i], pos, E.scale, n + 8, out=outs[i])
             else:
-                outs[i].copy_(dec[i].attn_decode(q[i], pos, E.scale, n + 8))
+                dec[i].attn_decode(q[i], pos, E.scale, n + 8, outs[i])
+
+    packed = torch.empty(QH * (D + 2), dtype=torch.float32, device=E.dev)
 
     def step_local():  # the same without the collective: partial + merge of the rank's own partial
         for i, L in enumerate(layers):
-            m, l, o = L.attn_decode_partial(q[i], pos, E.scale, n + 8)
-            outs[i].copy_(E.pkg.merge_partials(m.unsqueeze(0), l.unsqueeze(0), o.unsqueeze(0)))
+            L.attn_decode_partial_packed(q[i], pos, E.scale, n + 8, packed)
+            E.pkg.cache.merge_partials_packed(packed, 1, QH, D, outs[i])
 
-    run, graphed = E.graph(step)
+    # collectives are launched eagerly (not captured into a graph)
+    run, graphed = E.graph(step) if E.world == 1 else (step, False)
     with ClockSampler(E.local) as clk:
         for _ in range(max(args.warmup, 3)):
             run()
         ms = E.timed(run, args.steps)
-        run_l, _ = E.graph(step_local)
+        run_l, _ = E.graph(step_local) if E.world == 1 else (step_local, False)
         for _ in range(3):
             run_l()
         ms_local = E.timed(run_l, args.steps)

@@ -134,6 +134,11 @@ int kvb_attn_decode_partial(const kvb_layer* layer, const void* q, const int32_t
 int kvb_merge_partials(const float* parts_m, const float* parts_l, const float* parts_o, int parts, int q_heads,
                        int head_dim, int dtype, void* out, void* stream);
 
+/* Same merge for partials that travel as one block per part: block p = m[q_heads] | l[q_heads] | o[q_heads][head_dim]
+ * (q_heads * (head_dim + 2) floats), the layout one all-gather of kvb_attn_decode_partial outputs produces when
+ * part_m, part_l, part_o point into one send buffer.  No counterpart in the reference (single GPU). */
+int kvb_merge_partials_packed(const float* packed, int parts, int q_heads, int head_dim, int dtype, void* out, void* stream);
+
 /* MTP verify: append `width` (1..8) new rows, then causal attention of those rows (row i sees keys
  * 0..positions[i]).  q, out: [width][q_heads][head_dim]; k, v: [width][kv_heads][head_dim].
  * Replaces causal_attention_small_t_launch (P3:3508-3610). */

@@ -89,6 +89,15 @@ class KvarnLayer:
                                                        _ptr(o), _stream()))
         return m, l, o
 
+    def attn_decode_partial_packed(self, q, pos, scale, kv_len_max, packed):
+        """Partial into one caller buffer laid out m[QH] | l[QH] | o[QH, D] (fp32, QH * (D + 2) floats)."""
+        qh, d = self.q_heads, self.head_dim
+        base = packed.data_ptr()
+        capi.check(capi.load().kvb_attn_decode_partial(C.byref(self.c), _ptr(q), _ptr(pos), scale, kv_len_max, 0, 2**31 - 1,
+                                                       _ptr(self.workspace(kv_len_max, 1)), C.c_void_p(base),
+                                                       C.c_void_p(base + 4 * qh), C.c_void_p(base + 8 * qh), _stream()))
+        return packed
+
     # ---- causal_attention_small_t_launch (append + causal attention of 1..8 rows)
     def attn_verify(self, q, k, v, positions, scale, kv_len_max, out=None):
         out = torch.empty_like(q) if out is None else out
@@ -117,6 +126,14 @@ def merge_partials(m: torch.Tensor, l: torch.Tensor, o: torch.Tensor, dtype: tor
     capi.check(capi.load().kvb_merge_partials(_ptr(m.contiguous()), _ptr(l.contiguous()), _ptr(o.contiguous()), parts, qh, d,
                                               capi.DTYPE_BF16 if dtype == torch.bfloat16 else capi.DTYPE_F16, _ptr(out),
                                               _stream()))
+    return out
+
+
+def merge_partials_packed(packed: torch.Tensor, parts: int, q_heads: int, head_dim: int, out: torch.Tensor) -> torch.Tensor:
+    """packed: parts blocks of m[QH] | l[QH] | o[QH, D] -> out [q_heads, head_dim]."""
+    capi.check(capi.load().kvb_merge_partials_packed(_ptr(packed), parts, q_heads, head_dim,
+                                                     capi.DTYPE_BF16 if out.dtype == torch.bfloat16 else capi.DTYPE_F16,
+                                                     _ptr(out), _stream()))
     return out
 
 

@@ -624,21 +624,22 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
 }
 
 // Cross-GPU (or cross-range) merge of exported partials: parts_m in natural-log units.
+// Part p keeps its m and l at [p * ml_stride + row] and its o at [p * o_stride + row * D].
 __global__ void __launch_bounds__(128) merge_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
-                                                    const float* __restrict__ po, int parts, int rows, int dtype,
-                                                    uint16_t* __restrict__ out) {
+                                                    const float* __restrict__ po, int parts, int rows, int64_t ml_stride,
+                                                    int64_t o_stride, int dtype, uint16_t* __restrict__ out) {
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
     float m = -INFINITY;
-    for (int p = 0; p < parts; ++p) m = fmaxf(m, pm[static_cast<int64_t>(p) * rows + row]);
+    for (int p = 0; p < parts; ++p) m = fmaxf(m, pm[p * ml_stride + row]);
     float l = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (m != -INFINITY) {
         for (int p = 0; p < parts; ++p) {
-            const int64_t i = static_cast<int64_t>(p) * rows + row;
+            const int64_t i = p * ml_stride + row;
             const float w = __expf(pm[i] - m);
             l += w * pl[i];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o[j] += w * po[i * D + lane + 32 * j];
+            for (int j = 0; j < 4; ++j) o[j] += w * po[p * o_stride + static_cast<int64_t>(row) * D + lane + 32 * j];
         }
     }
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
@@ -769,7 +770,22 @@ extern "C" int kvb_merge_partials(const float* parts_m, const float* parts_l, co
         return fail(KVB_EINVAL, "kvb_merge_partials: null argument");
     if (parts < 1 || q_heads < 1) return fail(KVB_EINVAL, "kvb_merge_partials: parts %d / q_heads %d", parts, q_heads);
     if (head_dim != 128) return fail(KVB_ERANGE, "kvb_merge_partials: head_dim %d (128 supported)", head_dim);
-    merge_kernel<<<(q_heads + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(parts_m, parts_l, parts_o, parts, q_heads, dtype,
+    merge_kernel<<<(q_heads + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(parts_m, parts_l, parts_o, parts, q_heads, q_heads,
+                                                                                  static_cast<int64_t>(q_heads) * D, dtype,
+                                                                                  static_cast<uint16_t*>(out));
+    KVB_CUDA_OK(cudaGetLastError());
+    return KVB_OK;
+}
+
+extern "C" int kvb_merge_partials_packed(const float* packed, int parts, int q_heads, int head_dim, int dtype, void* out,
+                                         void* stream) {
+    using namespace kvb;
+    if (packed == nullptr || out == nullptr) return fail(KVB_EINVAL, "kvb_merge_partials_packed: null argument");
+    if (parts < 1 || q_heads < 1) return fail(KVB_EINVAL, "kvb_merge_partials_packed: parts %d / q_heads %d", parts, q_heads);
+    if (head_dim != 128) return fail(KVB_ERANGE, "kvb_merge_partials_packed: head_dim %d (128 supported)", head_dim);
+    const int64_t block = static_cast<int64_t>(q_heads) * (D + 2);
+    merge_kernel<<<(q_heads + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(packed, packed + q_heads, packed + 2 * q_heads, parts,
+                                                                                  q_heads, block, block, dtype,
                                                                                   static_cast<uint16_t*>(out));
     KVB_CUDA_OK(cudaGetLastError());
     return KVB_OK;
@@ -782,30 +798,6 @@ extern "C" int kvb_attn_verify(const kvb_layer* layer, const void* q, const void
     if (int st = kvb_append(layer, k, v, positions_dev, width, stream)) return st;
     return kvb::launch_attention(layer, q, positions_dev, positions_dev + (width - 1), width, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr,
                                  nullptr, static_cast<cudaStream_t>(stream), "kvb_attn_verify");
-}
-
-// First version of the prefill-chunk attention: quantise-append the chunk, then run the split-K kernel
-// over groups of 8 query tokens.  Correct for any chunk, but every group streams the whole prefix again.
-extern "C" size_t kvb_prefill_workspace_bytes(int kv_len_max, int kv_heads, int q_heads, int head_dim, int tokens) {
-    (void)tokens;
-    return kvb_workspace_bytes(kv_len_max, kv_heads, q_heads, head_dim, 8, 1);
-}
-
-extern "C" int kvb_attn_prefill(const kvb_layer* layer, const void* q, const void* k, const void* v,
-                                const int32_t* positions_dev, int tokens, float scale, int kv_len_max, void* workspace,
-                                void* out, void* stream) {
-    if (tokens < 1) return kvb::fail(KVB_EINVAL, "kvb_attn_prefill: tokens = %d", tokens);
-    if (int st = kvb_append(layer, k, v, positions_dev, tokens, stream)) return st;
-    const size_t row_bytes = static_cast<size_t>(layer->q_heads) * layer->head_dim * 2;
-    for (int t0 = 0; t0 < tokens; t0 += 8) {
-        const int w = tokens - t0 < 8 ? tokens - t0 : 8;
-        const int st = kvb::launch_attention(layer, static_cast<const char*>(q) + t0 * row_bytes, positions_dev + t0,
-                                             positions_dev + (tokens - 1), w, scale, kv_len_max, 0, INT_MAX, workspace,
-                                             static_cast<char*>(out) + t0 * row_bytes, nullptr, nullptr, nullptr,
-                                             static_cast<cudaStream_t>(stream), "kvb_attn_prefill");
-        if (st) return st;
-    }
-    return KVB_OK;
 }
 
 // ---------------------------------------------------------------------------------------------------------

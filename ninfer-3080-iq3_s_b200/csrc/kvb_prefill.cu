@@ -1,0 +1,397 @@
+// kvb_prefill.cu -- prefill-chunk attention over the quantised cache on the 5th-generation tensor cores.
+//
+// The chunk's (token, q head) rows of one KV head are GQA-packed into tiles of 128 rows; a CTA owns one such
+// tile, one KV head and one range of 128-key tiles, and walks its keys flash-attention style:
+//   S = Q K^T   tcgen05.mma, A = Q tile and B = de-quantised K tile in shared memory (K-major, 128-byte swizzle),
+//               accumulator S[128 x 128] fp32 in tensor memory;
+//   softmax     thread r owns row r (= TMEM lane r): loads S with tcgen05.ld, running max / sum in registers,
+//               writes P (fp16) to shared memory, rescales the O accumulator in TMEM only when a row maximum moved;
+//   O += P V    tcgen05.mma, A = P tile (K-major over keys), B = de-quantised V tile (MN-major: one 128-byte row
+//               of 64 dims per key), accumulator O[128 x 128] fp32 in tensor memory.
+// K and V tiles are de-quantised by the CUDA cores straight from the planes (thread = key): nibbles -> fp16 with
+// the exact unpack of the decode kernel, then one fused multiply-add with the tile's per-dim (K) or the key's
+// (V) fp16 scale and zero point.  Dims inside every group of eight are kept in the order the unpack yields
+// (0,4,1,5,2,6,3,7); Q is written in the same order, so the contraction is unaffected, and the merge kernel
+// puts the output dims back.  Keys of the open tile come un-quantised from the stage.
+// Every wait on an mbarrier is bounded; a wait that gives up sets KVB_ERR_WAIT_TIMEOUT and the CTA leaves
+// through the normal exit (TMEM is freed).
+#include <climits>
+
+#include "kvb_common.cuh"
+#include "kvb_tcgen05.cuh"
+
+namespace kvb {
+namespace {
+
+constexpr int D = 128;
+constexpr int kM = 128;        // query rows per CTA
+constexpr int kN = 128;        // keys per step = one quantisation tile
+constexpr int kThreads = 128;  // thread r <-> query row r <-> TMEM lane r
+constexpr int kTileBytes = kM * D * 2;
+constexpr uint32_t kTmemCols = 256;  // S at columns [0,128), O at [128,256)
+
+struct PrefillParams {
+    LayerView L;
+    const uint16_t* q;         // [T][q_heads][D]
+    const int32_t* pos;        // [T]
+    const int32_t* total_pos;  // newest position in the cache
+    int T, mtiles, ksplit;
+    float scale_log2;
+    float* ws_m;               // [H][mtiles][ksplit][128]
+    float* ws_l;
+    float* ws_o;               // [H][mtiles][ksplit][128][D], dims in tile order
+};
+
+struct __align__(1024) PrefillSmem {
+    uint8_t q[kTileBytes];
+    uint8_t k[kTileBytes];
+    uint8_t v[kTileBytes];
+    uint8_t p[kTileBytes];
+    __half ks[D], kz[D];  // per-dim scale / zero point of the K tile, in tile dim order
+    uint64_t bar_s, bar_o;
+    uint32_t tmem_base;
+    int row_pos[kM];
+    int flags[4];
+};
+
+// Byte offset of element (row, col) in a [128 rows][128 cols] fp16 tile stored as two 64-column blocks of
+// 128-byte rows, 8-row groups 1024 bytes apart, 16-byte chunks XOR-swizzled with the row (128-byte swizzle).
+__device__ __forceinline__ uint32_t tile_off(int row, int col) {
+    return (col >> 6) * 16384 + (row >> 3) * 1024 + (row & 7) * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4) + (col & 7) * 2;
+}
+// Position of dim d inside its group of eight: order 0,4,1,5,2,6,3,7.
+__device__ __forceinline__ int dim_slot(int d) { return (d & ~7) | ((d & 3) << 1) | ((d >> 2) & 1); }
+
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+
+// De-quantise one key row (64 code bytes) into the tile: out = code * scale + zp, pairs (d, d+4).
+// kPerDim: scale / zp pairs come from the per-dim tables (K); otherwise s2 / z2 hold the key's pair (V).
+template <bool kPerDim>
+__device__ __forceinline__ void dequant_row(const uint8_t* __restrict__ codes, uint8_t* tile, int row, const PrefillSmem& sm,
+                                            uint32_t s2, uint32_t z2) {
+    const uint4* src = reinterpret_cast<const uint4*>(codes);
+#pragma unroll
+    for (int v4 = 0; v4 < 4; ++v4) {
+        const uint4 pk = src[v4];
+        const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int chunk = v4 * 4 + i;  // dims 8 chunk .. 8 chunk + 7
+            uint32_t u[4];
+            unpack8(w[i], u);
+            uint4 out;
+            if constexpr (kPerDim) {
+                const uint4 sc = *reinterpret_cast<const uint4*>(&sm.ks[8 * chunk]);
+                const uint4 zp = *reinterpret_cast<const uint4*>(&sm.kz[8 * chunk]);
+                out = make_uint4(hfma2_u32(u[0], sc.x, zp.x), hfma2_u32(u[1], sc.y, zp.y), hfma2_u32(u[2], sc.z, zp.z),
+                                 hfma2_u32(u[3], sc.w, zp.w));
+            } else {
+                out = make_uint4(hfma2_u32(u[0], s2, z2), hfma2_u32(u[1], s2, z2), hfma2_u32(u[2], s2, z2), hfma2_u32(u[3], s2, z2));
+            }
+            *reinterpret_cast<uint4*>(tile + tile_off(row, 8 * chunk)) = out;
+        }
+    }
+}
+
+// Copy one un-quantised fp16 row of the stage into the tile (dims re-ordered inside every group of eight).
+__device__ __forceinline__ void stage_row_to_tile(const __half* __restrict__ src, uint8_t* tile, int row, bool live) {
+#pragma unroll
+    for (int chunk = 0; chunk < 16; ++chunk) {
+        uint4 r = live ? reinterpret_cast<const uint4*>(src)[chunk] : make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(tile + tile_off(row, 8 * chunk)) =
+            make_uint4(prmt(r.x, r.z, 0x5410), prmt(r.x, r.z, 0x7632), prmt(r.y, r.w, 0x5410), prmt(r.y, r.w, 0x7632));
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParams P) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    // the swizzled tiles need a 1024-byte aligned base; the launch reserves 1024 spare bytes for this
+    PrefillSmem& sm = *reinterpret_cast<PrefillSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
+    const LayerView& L = P.L;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int mt = blockIdx.x, head = blockIdx.y, zs = blockIdx.z;
+    const int G = L.q_heads / L.kv_heads;
+    const int kv_total = *P.total_pos + 1;
+
+    if (warp == 0) tc::tmem_alloc(&sm.tmem_base, kTmemCols);
+    if (tid == 0) {
+        mbar_init(&sm.bar_s, 1);
+        mbar_init(&sm.bar_o, 1);
+        mbar_fence_init();
+        sm.flags[0] = 0;
+    }
+    // ---- Q tile: rotate, scale, fp16, tile dim order.  One warp per row, lane l holds dims l + 32 j.
+    for (int r = warp; r < kM; r += kThreads / 32) {
+        const int R = mt * kM + r, tq = R / G, gq = R % G;
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        int rp = -1;
+        if (tq < P.T) {
+            const uint16_t* qrow = P.q + (static_cast<int64_t>(tq) * L.q_heads + head * G + gq) * D;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                v[j] = L.dtype == KVB_DTYPE_BF16 ? in_to_f32<true>(qrow[lane + 32 * j]) : in_to_f32<false>(qrow[lane + 32 * j]);
+            hadamard_warp<D>(v, lane);
+            rp = P.pos[tq];
+        }
+        if (lane == 0) sm.row_pos[r] = rp;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<__half*>(sm.q + tile_off(r, dim_slot(lane + 32 * j))) = __float2half_rn(v[j] * P.scale_log2);
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + kN;
+    const uint32_t lane_base = static_cast<uint32_t>(32 * warp) << 16;
+
+    int max_pos = -1, min_pos = INT_MAX;
+    for (int r = 0; r < kM; ++r) {
+        const int p = sm.row_pos[r];
+        if (p >= 0) { max_pos = max(max_pos, p); min_pos = min(min_pos, p); }
+    }
+    const int my_pos = sm.row_pos[tid];
+    // key tiles this CTA walks: those a row of the tile can see, cut into ksplit ranges
+    const int ntiles = max_pos < 0 ? 0 : min((kv_total + kN - 1) / kN, max_pos / kN + 1);
+    const int t0 = static_cast<int>(static_cast<int64_t>(ntiles) * zs / P.ksplit);
+    const int t1 = static_cast<int>(static_cast<int64_t>(ntiles) * (zs + 1) / P.ksplit);
+    const int32_t* tbl = L.table();
+    const uint32_t idesc_qk = tc::idesc_f16(kM, kN, false, false), idesc_pv = tc::idesc_f16(kM, D, false, true);
+    const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p);
+
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool have_o = false, failed = false;
+    uint32_t it = 0;
+    for (int t = t0; t < t1; ++t) {
+        const int base = t * kN;
+        const bool sealed = base + kN <= kv_total;
+        int32_t page = -1;
+        if (sealed) {
+            const int32_t pg0 = L.page_of(tbl, 2 * t), pg1 = L.page_of(tbl, 2 * t + 1);
+            if (pg0 < 0 || pg1 < 0) continue;  // reported in the error word; the tile is skipped by every thread alike
+            page = tid < 64 ? pg0 : pg1;
+            // per-dim scale / zero point of the tile (stored in both pages): page row d/2 = [s s z z other]
+            const __half* ksp = L.k_scale + page_head_offset(5, L.kv_heads, pg0, head);
+            sm.ks[dim_slot(tid)] = ksp[(tid >> 1) * 5 + (tid & 1)];
+            sm.kz[dim_slot(tid)] = ksp[(tid >> 1) * 5 + 2 + (tid & 1)];
+            __syncthreads();
+        }
+        // ---- K tile -> shared memory, then S = Q K^T on the tensor cores
+        if (sealed) {
+            dequant_row<true>(L.k_code + page_head_offset(64, L.kv_heads, page, head) + (tid & 63) * 64, sm.k, tid, sm, 0, 0);
+        } else {
+            stage_row_to_tile(L.stage_row(0, t & 1, head, tid), sm.k, tid, base + tid < kv_total);
+        }
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0) {
+            tc::fence_after_sync();
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                const uint32_t o = (kk >> 2) * 16384 + (kk & 3) * 32;
+                tc::mma_f16_ss(tmem_s, tc::smem_desc(q_addr + o, 16, 1024), tc::smem_desc(k_addr + o, 16, 1024), idesc_qk, kk > 0);
+            }
+            tc::commit(&sm.bar_s);
+        }
+        // ---- the previous P V must have drained before V, P and O are touched again
+        if (have_o && !mbar_wait_bounded(&sm.bar_o, (it - 1) & 1)) { failed = true; }
+        // ---- V tile -> shared memory (overlaps the QK MMA)
+        if (sealed) {
+            const __half* vsp = L.v_scale + page_head_offset(4, L.kv_heads, page, head) + (tid & 63) * 4;
+            const uint32_t sz = *reinterpret_cast<const uint32_t*>(vsp + 2);  // (scale, zp) of this key
+            dequant_row<false>(L.v_code + page_head_offset(64, L.kv_heads, page, head) + (tid & 63) * 64, sm.v, tid, sm,
+                               prmt(sz, sz, 0x1010), prmt(sz, sz, 0x3232));
+        } else {
+            stage_row_to_tile(L.stage_row(1, t & 1, head, tid), sm.v, tid, base + tid < kv_total);
+        }
+        // ---- softmax of row `tid`
+        if (!mbar_wait_bounded(&sm.bar_s, it & 1)) { failed = true; }
+        if (__syncthreads_or(failed)) { failed = true; break; }
+        tc::fence_after_sync();
+        float s[kN];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tc::tmem_ld32(tmem_s + lane_base + 32 * c, r);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) s[32 * c + j] = __uint_as_float(r[j]);
+        }
+        if (base + kN - 1 > min_pos || !sealed) {
+#pragma unroll
+            for (int j = 0; j < kN; ++j)
+                if (base + j > my_pos || base + j >= kv_total) s[j] = -INFINITY;
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < kN; ++j) mx = fmaxf(mx, s[j]);
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+        const float alpha = fast_exp2(m_run - m_use);
+        const bool moved = have_o && m_new > m_run;
+        m_run = m_new;
+        float sum = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            float p[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { p[j] = fast_exp2(s[8 * c + j] - m_use); sum += p[j]; }
+            *reinterpret_cast<uint4*>(sm.p + tile_off(tid, 8 * c)) =
+                make_uint4(pack_half2(p[0], p[1]), pack_half2(p[2], p[3]), pack_half2(p[4], p[5]), pack_half2(p[6], p[7]));
+        }
+        l_run = l_run * alpha + sum;
+        if (__any_sync(0xffffffffu, moved)) {  // rescale this warp's 32 rows of O (alpha = 1 for rows that did not move)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tc::tmem_ld32(tmem_o + lane_base + 32 * c, r);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+                tc::tmem_st32(tmem_o + lane_base + 32 * c, r);
+            }
+            tc::tmem_st_wait();
+        }
+        // ---- O += P V
+        fence_proxy_async();
+        tc::fence_before_sync();
+        __syncthreads();
+        if (tid == 0) {
+            tc::fence_after_sync();
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                const uint32_t po = (kk >> 2) * 16384 + (kk & 3) * 32;  // 16 keys along K of the P tile
+                tc::mma_f16_ss(tmem_o, tc::smem_desc(p_addr + po, 16, 1024), tc::smem_desc(v_addr + kk * 2048, 16384, 1024), idesc_pv,
+                               have_o || kk > 0);
+            }
+            tc::commit(&sm.bar_o);
+        }
+        have_o = true;
+        ++it;
+    }
+    if (have_o && !failed && !mbar_wait_bounded(&sm.bar_o, (it - 1) & 1)) failed = true;
+    if (failed && tid == 0) L.flag(KVB_ERR_WAIT_TIMEOUT);
+    tc::fence_after_sync();
+
+    // ---- partial of this (row tile, key range): m (log2 units), l, o in tile dim order
+    const int64_t idx = ((static_cast<int64_t>(head) * P.mtiles + mt) * P.ksplit + zs) * kM + tid;
+    P.ws_m[idx] = failed ? -INFINITY : m_run;
+    P.ws_l[idx] = failed ? 0.0f : l_run;
+    float* orow = P.ws_o + idx * D;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        if (have_o) {
+            tc::tmem_ld32(tmem_o + lane_base + 32 * c, r);
+            tc::tmem_ld_wait();
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(orow + 32 * c + j) =
+                have_o && !failed ? make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(sm.tmem_base, kTmemCols);
+}
+
+// Merge the key ranges of one query row, normalise, undo the tile dim order, rotate back, store.
+__global__ void __launch_bounds__(128) prefill_merge_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
+                                                            const float* __restrict__ ws_o, int T, int q_heads, int kv_heads,
+                                                            int mtiles, int ksplit, int dtype, uint16_t* __restrict__ out) {
+    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= T * q_heads) return;
+    const int G = q_heads / kv_heads, tq = row / q_heads, qh = row % q_heads, head = qh / G, R = tq * G + qh % G;
+    const int64_t base = ((static_cast<int64_t>(head) * mtiles + R / kM) * ksplit) * kM + R % kM;
+    float m = -INFINITY;
+    for (int z = 0; z < ksplit; ++z) m = fmaxf(m, ws_m[base + static_cast<int64_t>(z) * kM]);
+    float l = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (m != -INFINITY) {
+        for (int z = 0; z < ksplit; ++z) {
+            const int64_t i = base + static_cast<int64_t>(z) * kM;
+            const float w = fast_exp2(ws_m[i] - m);
+            l += w * ws_l[i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o[j] += w * ws_o[i * D + dim_slot(lane + 32 * j)];
+        }
+    }
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] *= inv;
+    hadamard_warp<D>(o, lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        out[static_cast<int64_t>(row) * D + lane + 32 * j] = dtype == KVB_DTYPE_BF16 ? f32_to_out<true>(o[j]) : f32_to_out<false>(o[j]);
+}
+
+int prefill_sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+void prefill_shape(int kv_len_max, int kv_heads, int q_heads, int tokens, int* mtiles, int* ksplit) {
+    const int rows = tokens * (q_heads / kv_heads);
+    *mtiles = (rows + kM - 1) / kM;
+    const int ctas = *mtiles * kv_heads, ntiles = (kv_len_max + kN - 1) / kN;
+    int ks = (4 * prefill_sm_count() + ctas - 1) / ctas;  // about four waves of CTAs
+    if (ks > ntiles / 2) ks = ntiles / 2;
+    if (ks > 32) ks = 32;
+    *ksplit = ks < 1 ? 1 : ks;
+}
+
+}  // namespace
+}  // namespace kvb
+
+extern "C" size_t kvb_prefill_workspace_bytes(int kv_len_max, int kv_heads, int q_heads, int head_dim, int tokens) {
+    if (kv_heads < 1 || q_heads < kv_heads || tokens < 1) return 0;
+    int mtiles, ksplit;
+    kvb::prefill_shape(kv_len_max, kv_heads, q_heads, tokens, &mtiles, &ksplit);
+    return static_cast<size_t>(kv_heads) * mtiles * ksplit * kvb::kM * (head_dim + 2) * sizeof(float);
+}
+
+extern "C" int kvb_attn_prefill(const kvb_layer* layer, const void* q, const void* k, const void* v,
+                                const int32_t* positions_dev, int tokens, float scale, int kv_len_max, void* workspace,
+                                void* out, void* stream) {
+    using namespace kvb;
+    if (int st = check_layer(layer, "kvb_attn_prefill")) return st;
+    if (tokens < 1) return fail(KVB_EINVAL, "kvb_attn_prefill: tokens = %d", tokens);
+    if (q == nullptr || workspace == nullptr || out == nullptr) return fail(KVB_EINVAL, "kvb_attn_prefill: null q / workspace / out");
+    if (layer->head_dim != 128) return fail(KVB_ERANGE, "kvb_attn_prefill: head_dim %d (the fused attention kernels cover 128)", layer->head_dim);
+    if (layer->sinkhorn_iters != 0)
+        return fail(KVB_ERANGE, "kvb_attn_prefill: sinkhorn_iters %d (the fused attention kernels cover the iters = 0 cache)", layer->sinkhorn_iters);
+    if (int st = kvb_append(layer, k, v, positions_dev, tokens, stream)) return st;
+    PrefillParams P;
+    P.L = make_view(*layer);
+    P.q = static_cast<const uint16_t*>(q);
+    P.pos = positions_dev;
+    P.total_pos = positions_dev + (tokens - 1);
+    P.T = tokens;
+    prefill_shape(kv_len_max, layer->kv_heads, layer->q_heads, tokens, &P.mtiles, &P.ksplit);
+    P.scale_log2 = scale * 1.4426950408889634f;
+    const size_t rows = static_cast<size_t>(layer->kv_heads) * P.mtiles * P.ksplit * kM;
+    P.ws_m = static_cast<float*>(workspace);
+    P.ws_l = P.ws_m + rows;
+    P.ws_o = P.ws_l + rows;
+    const int smem = static_cast<int>(sizeof(PrefillSmem)) + 1024;  // room to align the tiles to 1024 bytes
+    static bool opted = false;
+    if (!opted) {
+        KVB_CUDA_OK(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        opted = true;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    prefill_kernel<<<dim3(P.mtiles, layer->kv_heads, P.ksplit), kThreads, smem, s>>>(P);
+    KVB_CUDA_OK(cudaGetLastError());
+    const int total_rows = tokens * layer->q_heads;
+    prefill_merge_kernel<<<(total_rows + 3) / 4, 128, 0, s>>>(P.ws_m, P.ws_l, P.ws_o, tokens, layer->q_heads, layer->kv_heads, P.mtiles,
+                                                              P.ksplit, layer->dtype, static_cast<uint16_t*>(out));
+    KVB_CUDA_OK(cudaGetLastError());
+    return KVB_OK;
+}

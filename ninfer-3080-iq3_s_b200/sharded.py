@@ -66,15 +66,24 @@ def all_gather_partials(packed, group=None):
 
 class ShardedDecode:
     """Decode attention of one sequence whose cache is range-sharded over the ranks of `group`.
-    `layer` is this rank's local KvarnLayer holding `local_len` tokens (its range, local positions 0..)."""
+    `layer` is this rank's local KvarnLayer (its tile range, local positions 0..).  Three launches per call:
+    attention with partial export into the send buffer, one all-gather, the merge kernel."""
 
     def __init__(self, layer, group=None):
-        self.layer, self.group = layer, group
+        import torch
+        import torch.distributed as dist
 
-    def attn_decode(self, q, local_pos, scale: float, local_len_max: int, out_dtype=None):
+        self.layer, self.group = layer, group
+        self.world = dist.get_world_size(group)
+        n = layer.q_heads * (layer.head_dim + 2)
+        self.send = torch.empty(n, dtype=torch.float32, device=layer.device)
+        self.recv = torch.empty(self.world * n, dtype=torch.float32, device=layer.device)
+
+    def attn_decode(self, q, local_pos, scale: float, local_len_max: int, out):
+        import torch.distributed as dist
+
         from . import cache
 
-        m, l, o = self.layer.attn_decode_partial(q, local_pos, scale, local_len_max)
-        gathered = all_gather_partials(pack_partial(m, l, o), self.group)
-        gm, gl, go = unpack_partials(gathered)
-        return cache.merge_partials(gm, gl, go, dtype=out_dtype or self.layer.dtype)
+        self.layer.attn_decode_partial_packed(q, local_pos, scale, local_len_max, self.send)
+        dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
+        return cache.merge_partials_packed(self.recv, self.world, self.layer.q_heads, self.layer.head_dim, out)

@@ -86,8 +86,14 @@ class Twin:
         return np.array_equal(self.stage_np()[:, slot, :, :live], self.cpu.stage[:, slot, :, :live])
 
 
-def attn_close(got: np.ndarray, want: np.ndarray):
+# The prefill kernel rounds the de-quantised K and V tiles to fp16 before the tensor-core contraction (the decode
+# kernel keeps them exact and splits q instead): max-abs <= 2^-8 of the largest reference magnitude, rel-L2 <= 5e-3.
+PREFILL_MAX_ABS = 2.0 ** -8
+PREFILL_REL_L2 = 5e-3
+
+
+def attn_close(got: np.ndarray, want: np.ndarray, max_abs=ATTN_MAX_ABS, rel_l2=ATTN_REL_L2):
     err = float(np.abs(got.astype(np.float64) - want).max())
     ref = float(np.abs(want).max())
     rel = float(np.sqrt(((got.astype(np.float64) - want) ** 2).sum() / (want.astype(np.float64) ** 2).sum()))
-    return err <= ATTN_MAX_ABS * ref and rel <= ATTN_REL_L2, f"max-abs {err:.3e} (ref max {ref:.3e}, ratio {err / ref:.2e}), rel-L2 {rel:.2e}"
+    return err <= max_abs * ref and rel <= rel_l2, f"max-abs {err:.3e} (ref max {ref:.3e}, ratio {err / ref:.2e}), rel-L2 {rel:.2e}"

@@ -125,14 +125,20 @@ def test_partials_merge_to_the_full_answer():
     assert ok, msg
 
 
-def test_prefill_chunk_small():
+@pytest.mark.parametrize("prefix,chunk", [(333, 100), (0, 128), (1000, 300), (120, 8), (256, 1024), (77, 1)])
+def test_prefill_chunk(prefix, chunk):
+    """Quantise-append a chunk, then causal chunk attention over prefix + chunk on the tcgen05 kernel.  Covers a
+    chunk that starts the cache, chunks that complete tiles, an open tile left in the stage, a 1,024-token chunk."""
     import torch
 
-    H, QH, D, prefix, chunk = 4, 24, 128, 333, 100
+    from helpers import PREFILL_MAX_ABS, PREFILL_REL_L2
+
+    H, QH, D = 4, 24, 128
     T = prefix + chunk
     tw = Twin(D=D, H=H, QH=QH, capacity_tokens=T, seed=51)
     k, v = orc.synth_kv(52, T, H, D, 1), orc.synth_kv(52, T, H, D, 2)
-    tw.append(k[:prefix], v[:prefix])
+    if prefix:
+        tw.append(k[:prefix], v[:prefix])
     q = orc.synth_q(52, chunk, QH, D)
     pos = np.arange(prefix, T, dtype=np.int32)
     tw.cpu.append(k[prefix:], v[prefix:], prefix)
@@ -140,7 +146,13 @@ def test_prefill_chunk_small():
     out = tw.gpu.attn_prefill(torch.from_numpy(q).to(tw.dev), torch.from_numpy(k[prefix:]).to(tw.dev),
                               torch.from_numpy(v[prefix:]).to(tw.dev), torch.from_numpy(pos).to(tw.dev), 1.0 / np.sqrt(D), T)
     torch.cuda.synchronize()
-    ok, msg = attn_close(out.float().cpu().numpy(), want)
+    assert tw.gpu.errors() == 0
+    tw.len = T
+    eq = tw.planes_equal()
+    assert all(eq.values()), eq
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    ok, msg = attn_close(got, want, PREFILL_MAX_ABS, PREFILL_REL_L2)
     assert ok, msg
 
 
@@ -156,3 +168,26 @@ def test_bad_page_id_is_reported_not_faulted():
     out = _decode(tw, q[0], T - 1)
     assert np.isfinite(out).all()
     assert tw.gpu.errors() & pkg().capi.ERR_PAGE_RANGE
+
+
+def test_packed_partial_and_merge():
+    """The send-buffer layout of the sharded decode: m | l | o in one block per part."""
+    import torch
+
+    T = 900
+    tw = Twin(D=128, H=4, QH=24, capacity_tokens=T, seed=91)
+    k, v = orc.synth_kv(92, T, 4, 128, 1), orc.synth_kv(92, T, 4, 128, 2)
+    tw.append(k, v)
+    q = orc.synth_q(92, 1, 24, 128)
+    qd = torch.from_numpy(q[0]).to(tw.dev)
+    pos = torch.tensor([T - 1], dtype=torch.int32, device=tw.dev)
+    scale = 1.0 / np.sqrt(128)
+    n = 24 * 130
+    buf = torch.zeros(2 * n, dtype=torch.float32, device=tw.dev)
+    tw.gpu.attn_decode_partial_packed(qd, pos, scale, T, buf[:n])
+    buf[n:n + 24] = float("-inf")  # second part: a rank without keys (neutral partial)
+    out = torch.empty((24, 128), dtype=torch.float16, device=tw.dev)
+    pkg().cache.merge_partials_packed(buf, 2, 24, 128, out)
+    full = tw.gpu.attn_decode(qd, pos, scale, T)
+    torch.cuda.synchronize()
+    assert torch.equal(out, full)
