@@ -5,7 +5,8 @@
 //   S = Q K^T   tcgen05.mma, A = Q tile and B = de-quantised K tile in shared memory (K-major, 128-byte swizzle),
 //               accumulator S[128 x 128] fp32 in tensor memory;
 //   softmax     thread r owns row r (= TMEM lane r): loads S with tcgen05.ld, running max / sum in registers,
-//               writes P (fp16) to shared memory, rescales the O accumulator in TMEM only when a row maximum moved;
+//               writes P (fp16) over the K tile (S is complete by then), rescales the O accumulator in TMEM only
+//               when a row maximum moved;
 //   O += P V    tcgen05.mma, A = P tile (K-major over keys), B = de-quantised V tile (MN-major: one 128-byte row
 //               of 64 dims per key), accumulator O[128 x 128] fp32 in tensor memory.
 // K and V tiles are de-quantised by the CUDA cores straight from the planes (thread = key): nibbles -> fp16 with
@@ -13,6 +14,8 @@
 // (V) fp16 scale and zero point.  Dims inside every group of eight are kept in the order the unpack yields
 // (0,4,1,5,2,6,3,7); Q is written in the same order, so the contraction is unaffected, and the merge kernel
 // puts the output dims back.  Keys of the open tile come un-quantised from the stage.
+// Three 32 KB tiles (Q, K/P, V) and 256 TMEM columns per CTA let two CTAs share an SM, so one CTA's CUDA-core
+// phases (de-quantisation, softmax) overlap the other's MMAs.
 // Every wait on an mbarrier is bounded; a wait that gives up sets KVB_ERR_WAIT_TIMEOUT and the CTA leaves
 // through the normal exit (TMEM is freed).
 #include <climits>
@@ -44,9 +47,8 @@ struct PrefillParams {
 
 struct __align__(1024) PrefillSmem {
     uint8_t q[kTileBytes];
-    uint8_t k[kTileBytes];
+    uint8_t k[kTileBytes];  // the K tile, then -- once S = Q K^T has completed -- the P tile of the same step
     uint8_t v[kTileBytes];
-    uint8_t p[kTileBytes];
     __half ks[D], kz[D];  // per-dim scale / zero point of the K tile, in tile dim order
     uint64_t bar_s, bar_o;
     uint32_t tmem_base;
@@ -107,7 +109,7 @@ __device__ __forceinline__ void stage_row_to_tile(const __half* __restrict__ src
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParams P) {
+__global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParams P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // the swizzled tiles need a 1024-byte aligned base; the launch reserves 1024 spare bytes for this
     PrefillSmem& sm = *reinterpret_cast<PrefillSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
@@ -160,7 +162,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
     const int t1 = static_cast<int>(static_cast<int64_t>(ntiles) * (zs + 1) / P.ksplit);
     const int32_t* tbl = L.table();
     const uint32_t idesc_qk = tc::idesc_f16(kM, kN, false, false), idesc_pv = tc::idesc_f16(kM, D, false, true);
-    const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p);
+    const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), p_addr = k_addr;
 
     float m_run = -INFINITY, l_run = 0.0f;
     bool have_o = false, failed = false;
@@ -179,6 +181,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
             sm.kz[dim_slot(tid)] = ksp[(tid >> 1) * 5 + 2 + (tid & 1)];
             __syncthreads();
         }
+        // ---- the previous P V reads P from the K/P buffer and V from its own: it must have drained first
+        if (have_o && !mbar_wait_bounded(&sm.bar_o, (it - 1) & 1)) { failed = true; }
         // ---- K tile -> shared memory, then S = Q K^T on the tensor cores
         if (sealed) {
             dequant_row<true>(L.k_code + page_head_offset(64, L.kv_heads, page, head) + (tid & 63) * 64, sm.k, tid, sm, 0, 0);
@@ -196,8 +200,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
             }
             tc::commit(&sm.bar_s);
         }
-        // ---- the previous P V must have drained before V, P and O are touched again
-        if (have_o && !mbar_wait_bounded(&sm.bar_o, (it - 1) & 1)) { failed = true; }
         // ---- V tile -> shared memory (overlaps the QK MMA)
         if (sealed) {
             const __half* vsp = L.v_scale + page_head_offset(4, L.kv_heads, page, head) + (tid & 63) * 4;
@@ -239,7 +241,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_kernel(const PrefillParam
             float p[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) { p[j] = fast_exp2(s[8 * c + j] - m_use); sum += p[j]; }
-            *reinterpret_cast<uint4*>(sm.p + tile_off(tid, 8 * c)) =
+            *reinterpret_cast<uint4*>(sm.k + tile_off(tid, 8 * c)) =
                 make_uint4(pack_half2(p[0], p[1]), pack_half2(p[2], p[3]), pack_half2(p[4], p[5]), pack_half2(p[6], p[7]));
         }
         l_run = l_run * alpha + sum;
@@ -341,7 +343,7 @@ void prefill_shape(int kv_len_max, int kv_heads, int q_heads, int tokens, int* m
     const int rows = tokens * (q_heads / kv_heads);
     *mtiles = (rows + kM - 1) / kM;
     const int ctas = *mtiles * kv_heads, ntiles = (kv_len_max + kN - 1) / kN;
-    int ks = (4 * prefill_sm_count() + ctas - 1) / ctas;  // about four waves of CTAs
+    int ks = (8 * prefill_sm_count() + ctas - 1) / ctas;  // about four waves of CTAs at two CTAs per SM
     if (ks > ntiles / 2) ks = ntiles / 2;
     if (ks > 32) ks = 32;
     *ksplit = ks < 1 ? 1 : ks;
