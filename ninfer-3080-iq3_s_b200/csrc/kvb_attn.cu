@@ -735,6 +735,8 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
 }  // namespace
 }  // namespace kvb
 
+// From this many GQA-merged query rows per KV head on, the contraction is dense enough for the tcgen05 kernel.
+static constexpr int kDenseRows = 16;
 extern "C" int kvb_split_capacity(int kv_len_max, int kv_heads, int q_heads, int rows, int batch) {
     (void)batch;
     if (kv_heads < 1 || q_heads < kv_heads || rows < 1) return 0;
@@ -745,7 +747,12 @@ extern "C" size_t kvb_workspace_bytes(int kv_len_max, int kv_heads, int q_heads,
     if (kv_heads < 1 || q_heads < kv_heads || rows < 1 || batch < 1) return 0;
     const int Z = kvb::zblocks_of(q_heads, kv_heads, rows);
     const size_t parts = kvb::split_count(kv_len_max, kv_heads, Z) + 1;
-    return static_cast<size_t>(batch) * kv_heads * Z * parts * kvb::kRows * (head_dim + 2) * sizeof(float);
+    size_t bytes = static_cast<size_t>(kv_heads) * Z * parts * kvb::kRows * (head_dim + 2) * sizeof(float);
+    if (rows * (q_heads / kv_heads) >= kDenseRows) {  // verify steps this wide run on the chunk-attention kernel
+        const size_t dense = kvb_prefill_workspace_bytes(kv_len_max, kv_heads, q_heads, head_dim, rows);
+        if (dense > bytes) bytes = dense;
+    }
+    return static_cast<size_t>(batch) * bytes;
 }
 
 extern "C" int kvb_attn_decode(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
@@ -791,11 +798,21 @@ extern "C" int kvb_merge_partials_packed(const float* packed, int parts, int q_h
     return KVB_OK;
 }
 
+namespace kvb {
+int launch_chunk_attention(const kvb_layer* layer, const void* q, const int32_t* positions_dev, int tokens, float scale,
+                           int kv_len_max, void* workspace, void* out, cudaStream_t s);  // kvb_prefill.cu
+}
+
 extern "C" int kvb_attn_verify(const kvb_layer* layer, const void* q, const void* k, const void* v,
                                const int32_t* positions_dev, int width, float scale, int kv_len_max, void* workspace,
                                void* out, void* stream) {
     if (width < 1 || width > 8) return kvb::fail(KVB_ERANGE, "kvb_attn_verify: width %d (1..8; the reference rejects more, too)", width);
+    if (int st = kvb::check_layer(layer, "kvb_attn_verify")) return st;
     if (int st = kvb_append(layer, k, v, positions_dev, width, stream)) return st;
+    if (width * (layer->q_heads / layer->kv_heads) >= kDenseRows && layer->head_dim == 128 && layer->sinkhorn_iters == 0) {
+        if (q == nullptr || workspace == nullptr || out == nullptr) return kvb::fail(KVB_EINVAL, "kvb_attn_verify: null q / workspace / out");
+        return kvb::launch_chunk_attention(layer, q, positions_dev, width, scale, kv_len_max, workspace, out, static_cast<cudaStream_t>(stream));
+    }
     return kvb::launch_attention(layer, q, positions_dev, positions_dev + (width - 1), width, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr,
                                  nullptr, static_cast<cudaStream_t>(stream), "kvb_attn_verify");
 }

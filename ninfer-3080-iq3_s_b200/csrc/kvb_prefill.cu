@@ -73,12 +73,11 @@ __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c
 // De-quantise one key row (64 code bytes) into the tile: out = code * scale + zp, pairs (d, d+4).
 // kPerDim: scale / zp pairs come from the per-dim tables (K); otherwise s2 / z2 hold the key's pair (V).
 template <bool kPerDim>
-__device__ __forceinline__ void dequant_row(const uint8_t* __restrict__ codes, uint8_t* tile, int row, const PrefillSmem& sm,
+__device__ __forceinline__ void dequant_row(const uint4 (&codes)[4], uint8_t* tile, int row, const PrefillSmem& sm,
                                             uint32_t s2, uint32_t z2) {
-    const uint4* src = reinterpret_cast<const uint4*>(codes);
 #pragma unroll
     for (int v4 = 0; v4 < 4; ++v4) {
-        const uint4 pk = src[v4];
+        const uint4 pk = codes[v4];
         const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -167,25 +166,56 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     float m_run = -INFINITY, l_run = 0.0f;
     bool have_o = false, failed = false;
     uint32_t it = 0;
+    const bool warp_has_rows = __any_sync(0xffffffffu, my_pos >= 0);  // warps without a valid row skip the softmax
+
+    // Everything a tile needs from global memory before its K side can be de-quantised; fetched one tile ahead
+    // so that the page-table lookup and the load latency hide behind the previous tile's softmax.
+    struct KFetch {
+        uint4 codes[4];
+        __half ks, kz;
+        int32_t page;  // page of this thread's key (-1: tile unusable)
+        bool sealed, ok;
+    };
+    auto fetch_k = [&](int t, KFetch& f) {
+        f.sealed = t * kN + kN <= kv_total;
+        f.ok = t < t1;
+        f.page = -1;
+        if (!f.ok || !f.sealed) return;
+        const int32_t pg0 = L.page_of(tbl, 2 * t), pg1 = L.page_of(tbl, 2 * t + 1);
+        if (pg0 < 0 || pg1 < 0) { f.ok = false; return; }  // reported in the error word; every thread skips the tile alike
+        f.page = tid < 64 ? pg0 : pg1;
+        const uint4* kc = reinterpret_cast<const uint4*>(L.k_code + page_head_offset(64, L.kv_heads, f.page, head) + (tid & 63) * 64);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f.codes[i] = kc[i];
+        // per-dim scale / zero point of the tile (stored in both pages): page row d/2 = [s s z z other]
+        const __half* ksp = L.k_scale + page_head_offset(5, L.kv_heads, pg0, head);
+        f.ks = ksp[(tid >> 1) * 5 + (tid & 1)];
+        f.kz = ksp[(tid >> 1) * 5 + 2 + (tid & 1)];
+    };
+    KFetch cur, nxt;
+    fetch_k(t0, nxt);
     for (int t = t0; t < t1; ++t) {
+        cur = nxt;
         const int base = t * kN;
-        const bool sealed = base + kN <= kv_total;
-        int32_t page = -1;
+        const bool sealed = cur.sealed;
+        if (!cur.ok) { fetch_k(t + 1, nxt); continue; }
+        // V side of this tile: issue the loads now, use them after the K side
+        uint4 vcodes[4];
+        uint32_t vsz = 0;
         if (sealed) {
-            const int32_t pg0 = L.page_of(tbl, 2 * t), pg1 = L.page_of(tbl, 2 * t + 1);
-            if (pg0 < 0 || pg1 < 0) continue;  // reported in the error word; the tile is skipped by every thread alike
-            page = tid < 64 ? pg0 : pg1;
-            // per-dim scale / zero point of the tile (stored in both pages): page row d/2 = [s s z z other]
-            const __half* ksp = L.k_scale + page_head_offset(5, L.kv_heads, pg0, head);
-            sm.ks[dim_slot(tid)] = ksp[(tid >> 1) * 5 + (tid & 1)];
-            sm.kz[dim_slot(tid)] = ksp[(tid >> 1) * 5 + 2 + (tid & 1)];
-            __syncthreads();
+            const uint4* vc = reinterpret_cast<const uint4*>(L.v_code + page_head_offset(64, L.kv_heads, cur.page, head) + (tid & 63) * 64);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) vcodes[i] = vc[i];
+            vsz = *reinterpret_cast<const uint32_t*>(L.v_scale + page_head_offset(4, L.kv_heads, cur.page, head) + (tid & 63) * 4 + 2);
+            sm.ks[dim_slot(tid)] = cur.ks;
+            sm.kz[dim_slot(tid)] = cur.kz;
         }
         // ---- the previous P V reads P from the K/P buffer and V from its own: it must have drained first
         if (have_o && !mbar_wait_bounded(&sm.bar_o, (it - 1) & 1)) { failed = true; }
+        __syncthreads();  // scale tables visible; nobody still reads the previous tile's tables
         // ---- K tile -> shared memory, then S = Q K^T on the tensor cores
         if (sealed) {
-            dequant_row<true>(L.k_code + page_head_offset(64, L.kv_heads, page, head) + (tid & 63) * 64, sm.k, tid, sm, 0, 0);
+            dequant_row<true>(cur.codes, sm.k, tid, sm, 0, 0);
         } else {
             stage_row_to_tile(L.stage_row(0, t & 1, head, tid), sm.k, tid, base + tid < kv_total);
         }
@@ -200,19 +230,18 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
             }
             tc::commit(&sm.bar_s);
         }
-        // ---- V tile -> shared memory (overlaps the QK MMA)
+        // ---- V tile -> shared memory (overlaps the QK MMA), then start fetching the next tile
         if (sealed) {
-            const __half* vsp = L.v_scale + page_head_offset(4, L.kv_heads, page, head) + (tid & 63) * 4;
-            const uint32_t sz = *reinterpret_cast<const uint32_t*>(vsp + 2);  // (scale, zp) of this key
-            dequant_row<false>(L.v_code + page_head_offset(64, L.kv_heads, page, head) + (tid & 63) * 64, sm.v, tid, sm,
-                               prmt(sz, sz, 0x1010), prmt(sz, sz, 0x3232));
+            dequant_row<false>(vcodes, sm.v, tid, sm, prmt(vsz, vsz, 0x1010), prmt(vsz, vsz, 0x3232));
         } else {
             stage_row_to_tile(L.stage_row(1, t & 1, head, tid), sm.v, tid, base + tid < kv_total);
         }
+        fetch_k(t + 1, nxt);
         // ---- softmax of row `tid`
         if (!mbar_wait_bounded(&sm.bar_s, it & 1)) { failed = true; }
         if (__syncthreads_or(failed)) { failed = true; break; }
         tc::fence_after_sync();
+        if (warp_has_rows) {
         float s[kN];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -257,6 +286,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
             }
             tc::tmem_st_wait();
         }
+        }  // warp_has_rows (rows of the other warps are never read: their P and O may hold anything)
         // ---- O += P V
         fence_proxy_async();
         tc::fence_before_sync();
@@ -280,16 +310,20 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
 
     // ---- partial of this (row tile, key range): m (log2 units), l, o in tile dim order
     const int64_t idx = ((static_cast<int64_t>(head) * P.mtiles + mt) * P.ksplit + zs) * kM + tid;
-    P.ws_m[idx] = failed ? -INFINITY : m_run;
-    P.ws_l[idx] = failed ? 0.0f : l_run;
+    if (my_pos >= 0) {
+        P.ws_m[idx] = failed ? -INFINITY : m_run;
+        P.ws_l[idx] = failed ? 0.0f : l_run;
+    }
     float* orow = P.ws_o + idx * D;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
+        if (!warp_has_rows) break;
         uint32_t r[32];
         if (have_o) {
             tc::tmem_ld32(tmem_o + lane_base + 32 * c, r);
             tc::tmem_ld_wait();
         }
+        if (my_pos < 0) continue;
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
             *reinterpret_cast<float4*>(orow + 32 * c + j) =
@@ -302,24 +336,44 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
 }
 
 // Merge the key ranges of one query row, normalise, undo the tile dim order, rotate back, store.
-__global__ void __launch_bounds__(128) prefill_merge_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
+// One CTA of 8 warps per row: warp w takes ranges w, w+8, ..; lane l owns dims l + 32 j.  The loop is pure load
+// latency, so it is unrolled to keep several ranges in flight; the warp sums meet in shared memory.
+__global__ void __launch_bounds__(256) prefill_merge_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
                                                             const float* __restrict__ ws_o, int T, int q_heads, int kv_heads,
                                                             int mtiles, int ksplit, int dtype, uint16_t* __restrict__ out) {
-    const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= T * q_heads) return;
+    __shared__ float so[8][D];
+    __shared__ float sl[8];
+    const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = q_heads / kv_heads, tq = row / q_heads, qh = row % q_heads, head = qh / G, R = tq * G + qh % G;
     const int64_t base = ((static_cast<int64_t>(head) * mtiles + R / kM) * ksplit) * kM + R % kM;
     float m = -INFINITY;
-    for (int z = 0; z < ksplit; ++z) m = fmaxf(m, ws_m[base + static_cast<int64_t>(z) * kM]);
+    for (int z = lane; z < ksplit; z += 32) m = fmaxf(m, ws_m[base + static_cast<int64_t>(z) * kM]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     float l = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (m != -INFINITY) {
-        for (int z = 0; z < ksplit; ++z) {
+#pragma unroll 4
+        for (int z = warp; z < ksplit; z += 8) {
             const int64_t i = base + static_cast<int64_t>(z) * kM;
             const float w = fast_exp2(ws_m[i] - m);
             l += w * ws_l[i];
 #pragma unroll
             for (int j = 0; j < 4; ++j) o[j] += w * ws_o[i * D + dim_slot(lane + 32 * j)];
         }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) so[warp][lane + 32 * j] = o[j];
+    if (lane == 0) sl[warp] = l;
+    __syncthreads();
+    if (warp != 0) return;
+    l = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        l += sl[w];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] += so[w][lane + 32 * j];
     }
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
 #pragma unroll
@@ -343,9 +397,12 @@ void prefill_shape(int kv_len_max, int kv_heads, int q_heads, int tokens, int* m
     const int rows = tokens * (q_heads / kv_heads);
     *mtiles = (rows + kM - 1) / kM;
     const int ctas = *mtiles * kv_heads, ntiles = (kv_len_max + kN - 1) / kN;
-    int ks = (8 * prefill_sm_count() + ctas - 1) / ctas;  // about four waves of CTAs at two CTAs per SM
+    // two CTAs share an SM: about four waves of CTAs for a chunk (load balance), one wave for a few rows (verify),
+    // where every extra key range costs a partial per row
+    const int waves = ctas >= 64 ? 4 : 1;
+    int ks = (waves * 2 * prefill_sm_count() + ctas - 1) / ctas;
     if (ks > ntiles / 2) ks = ntiles / 2;
-    if (ks > 32) ks = 32;
+    if (ks > 128) ks = 128;
     *ksplit = ks < 1 ? 1 : ks;
 }
 
@@ -359,17 +416,10 @@ extern "C" size_t kvb_prefill_workspace_bytes(int kv_len_max, int kv_heads, int 
     return static_cast<size_t>(kv_heads) * mtiles * ksplit * kvb::kM * (head_dim + 2) * sizeof(float);
 }
 
-extern "C" int kvb_attn_prefill(const kvb_layer* layer, const void* q, const void* k, const void* v,
-                                const int32_t* positions_dev, int tokens, float scale, int kv_len_max, void* workspace,
-                                void* out, void* stream) {
-    using namespace kvb;
-    if (int st = check_layer(layer, "kvb_attn_prefill")) return st;
-    if (tokens < 1) return fail(KVB_EINVAL, "kvb_attn_prefill: tokens = %d", tokens);
-    if (q == nullptr || workspace == nullptr || out == nullptr) return fail(KVB_EINVAL, "kvb_attn_prefill: null q / workspace / out");
-    if (layer->head_dim != 128) return fail(KVB_ERANGE, "kvb_attn_prefill: head_dim %d (the fused attention kernels cover 128)", layer->head_dim);
-    if (layer->sinkhorn_iters != 0)
-        return fail(KVB_ERANGE, "kvb_attn_prefill: sinkhorn_iters %d (the fused attention kernels cover the iters = 0 cache)", layer->sinkhorn_iters);
-    if (int st = kvb_append(layer, k, v, positions_dev, tokens, stream)) return st;
+namespace kvb {
+// Chunk attention of `tokens` rows that are already appended (shared by the prefill and the verify entry points).
+int launch_chunk_attention(const kvb_layer* layer, const void* q, const int32_t* positions_dev, int tokens, float scale,
+                           int kv_len_max, void* workspace, void* out, cudaStream_t s) {
     PrefillParams P;
     P.L = make_view(*layer);
     P.q = static_cast<const uint16_t*>(q);
@@ -388,12 +438,26 @@ extern "C" int kvb_attn_prefill(const kvb_layer* layer, const void* q, const voi
         KVB_CUDA_OK(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         opted = true;
     }
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     prefill_kernel<<<dim3(P.mtiles, layer->kv_heads, P.ksplit), kThreads, smem, s>>>(P);
     KVB_CUDA_OK(cudaGetLastError());
     const int total_rows = tokens * layer->q_heads;
-    prefill_merge_kernel<<<(total_rows + 3) / 4, 128, 0, s>>>(P.ws_m, P.ws_l, P.ws_o, tokens, layer->q_heads, layer->kv_heads, P.mtiles,
-                                                              P.ksplit, layer->dtype, static_cast<uint16_t*>(out));
+    prefill_merge_kernel<<<total_rows, 256, 0, s>>>(P.ws_m, P.ws_l, P.ws_o, tokens, layer->q_heads, layer->kv_heads, P.mtiles,
+                                                    P.ksplit, layer->dtype, static_cast<uint16_t*>(out));
     KVB_CUDA_OK(cudaGetLastError());
     return KVB_OK;
+}
+}  // namespace kvb
+
+extern "C" int kvb_attn_prefill(const kvb_layer* layer, const void* q, const void* k, const void* v,
+                                const int32_t* positions_dev, int tokens, float scale, int kv_len_max, void* workspace,
+                                void* out, void* stream) {
+    using namespace kvb;
+    if (int st = check_layer(layer, "kvb_attn_prefill")) return st;
+    if (tokens < 1) return fail(KVB_EINVAL, "kvb_attn_prefill: tokens = %d", tokens);
+    if (q == nullptr || workspace == nullptr || out == nullptr) return fail(KVB_EINVAL, "kvb_attn_prefill: null q / workspace / out");
+    if (layer->head_dim != 128) return fail(KVB_ERANGE, "kvb_attn_prefill: head_dim %d (the fused attention kernels cover 128)", layer->head_dim);
+    if (layer->sinkhorn_iters != 0)
+        return fail(KVB_ERANGE, "kvb_attn_prefill: sinkhorn_iters %d (the fused attention kernels cover the iters = 0 cache)", layer->sinkhorn_iters);
+    if (int st = kvb_append(layer, k, v, positions_dev, tokens, stream)) return st;
+    return launch_chunk_attention(layer, q, positions_dev, tokens, scale, kv_len_max, workspace, out, static_cast<cudaStream_t>(stream));
 }

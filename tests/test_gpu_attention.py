@@ -92,7 +92,10 @@ def test_verify_rows_are_causal(prefix, width):
     tw.len = T
     eq = tw.planes_equal()
     assert all(eq.values()), eq
-    ok, msg = attn_close(out.float().cpu().numpy(), want)
+    # from 16 GQA-merged rows per KV head on (width >= 3 here) the step runs on the tcgen05 chunk kernel
+    from helpers import PREFILL_MAX_ABS, PREFILL_REL_L2
+    dense = width * (QH // H) >= 16
+    ok, msg = attn_close(out.float().cpu().numpy(), want, PREFILL_MAX_ABS if dense else 2.0 ** -10, PREFILL_REL_L2 if dense else 1e-3)
     assert ok, msg
 
 
