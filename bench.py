@@ -467,6 +467,43 @@ def run_long(args):
     })
 
 
+def run_decode_ctx(args):
+    """Decode attention alone (no append) at --ctx tokens over --layers layers; the case the ncu captures use."""
+    E = _Env()
+    torch = E.torch
+    ctx = args.ctx or 131072
+    layers_n = args.layers or max(2, min(16, int(400e6 // (ctx * H * 146)) + 1))
+    layers = [E.layer(ctx, 8, i) for i in range(layers_n)]
+    q = torch.randn((layers_n, QH, D), generator=E.gen, device=E.dev).to(torch.float16)
+    pos = torch.full((1,), ctx - 1, dtype=torch.int32, device=E.dev)
+    outs = torch.empty((layers_n, QH, D), dtype=torch.float16, device=E.dev)
+    for L in layers:
+        L.workspace(ctx + 8, 1)
+
+    def step():
+        for i, L in enumerate(layers):
+            L.attn_decode(q[i], pos, E.scale, ctx + 8, out=outs[i])
+
+    run, graphed = E.graph(step)
+    with ClockSampler(E.local) as clk:
+        for _ in range(max(args.warmup, 3)):
+            run()
+        ms = E.timed(run, args.steps)
+    peak, kind = peaks()
+    us = ms * 1e3 / layers_n
+    nbytes = decode_bytes(ctx)
+    E.finish({
+        "metric": "decode_attn_hbm_gbs", "value": nbytes / (us * 1e-6) / 1e9, "unit": "GB/s", "n_gpus": E.world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "us_per_layer": us, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"decode_attention_only_ctx{ctx}", "layers": layers_n, "q_heads": QH, "kv_heads": H, "head_dim": D,
+                   "l2": f"{layers_n} layers x {ctx * H * 146 / 1e6:.0f} MB between revisits"},
+        "roofline": {"bound": "hbm", "achieved": nbytes / (us * 1e-6) / 1e9, "peak": peak, "peak_kind": kind, "unit": "GB/s",
+                     "frac": nbytes / (us * 1e-6) / 1e9 / peak, "traffic": TRAFFIC_BYTES_PER_TOKEN * ctx},
+        "graph_captured": graphed, "clocks": clk.summary(), "gpu_launches": args.steps * layers_n * 2,
+    })
+
+
 def run_batch(args):
     """BASELINE config 4B: 32 independent sequences, lengths seed-uniform in 16K..131K, sharded by sequence; one
     layer per sequence, a step = one decode call per local sequence."""
@@ -600,17 +637,17 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="decode32k", choices=["decode32k", "long379k", "batch32", "verify131k", "prefill262k"],
+    ap.add_argument("--workload", default="decode32k", choices=["decode32k", "decodectx", "long379k", "batch32", "verify131k", "prefill262k"],
                     help="decode32k is the contract line; the others are BASELINE configs 4A, 4B, 2 and 3")
     ap.add_argument("--layers", type=int, default=0, help="layers held for long379k / verify131k (default 4)")
-    ap.add_argument("--ctx", type=int, default=0, help="prefix length for prefill262k (default 262144)")
+    ap.add_argument("--ctx", type=int, default=0, help="context for decodectx (default 131072) / prefix length for prefill262k (default 262144)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "decode32k":
         run_gpu(args)
     else:
-        {"long379k": run_long, "batch32": run_batch, "verify131k": run_verify, "prefill262k": run_prefill}[args.workload](args)
+        {"decodectx": run_decode_ctx, "long379k": run_long, "batch32": run_batch, "verify131k": run_verify, "prefill262k": run_prefill}[args.workload](args)
 
 
 if __name__ == "__main__":
