@@ -126,6 +126,73 @@ __device__ __forceinline__ void build_qfrag(const AttnSmem& sm, const uint8_t* s
     }
 }
 
+// Integer form of (q' * scale_K)^T for the quantised pages: each row is scaled to 16-bit integers
+// (row scale f = max|.| / 32639) and split into two signed 8-bit digits, Qi = 256 hi + lo, so that the key side
+// can feed its packed code bytes to the int8 tensor path without unpacking nibbles: with L = byte & 0x0F (even
+// dim) and H = byte & 0xF0 (16 x odd dim),   sum_d Qi[d] code[d] = sum_b Qi[2b] L_b + (1/16) sum_b Qi[2b+1] H_b.
+// b[nb][kb][part][digit] holds the B fragments (b0, b1) of 32-byte k-block kb: part 0 = even dims, 1 = odd dims.
+template <int NB> struct QInt {
+    uint32_t b[NB][2][2][2][2];
+    float f[NB][2];   // row scale / 16 of the lane's rows 2t, 2t+1
+    float qz[NB][2];  // sum_d q'[row][d] * zp_K[d]
+};
+
+__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NB>
+__device__ __forceinline__ void build_qint(const AttnSmem& sm, const uint8_t* scratch, int lane, QInt<NB>& f) {
+    const int t = lane & 3;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        float qs[32];
+        float qz = 0.0f, amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float4 qv = sm.qfrag[nb][j][lane];
+            const uint2 ks = *reinterpret_cast<const uint2*>(scratch + (32 * t + 4 * j) * 2);
+            const uint2 kz = *reinterpret_cast<const uint2*>(scratch + 256 + (32 * t + 4 * j) * 2);
+            const float2 s01 = unpack_half2(ks.x), s23 = unpack_half2(ks.y);
+            const float2 z01 = unpack_half2(kz.x), z23 = unpack_half2(kz.y);
+            qs[4 * j + 0] = qv.x * s01.x; qs[4 * j + 1] = qv.y * s01.y;
+            qs[4 * j + 2] = qv.z * s23.x; qs[4 * j + 3] = qv.w * s23.y;
+            qz = fmaf(qv.x, z01.x, qz); qz = fmaf(qv.y, z01.y, qz);
+            qz = fmaf(qv.z, z23.x, qz); qz = fmaf(qv.w, z23.y, qz);
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(qs[4 * j]), fabsf(qs[4 * j + 1]))), fmaxf(fabsf(qs[4 * j + 2]), fabsf(qs[4 * j + 3])));
+        }
+        qz += __shfl_xor_sync(0xffffffffu, qz, 1);
+        qz += __shfl_xor_sync(0xffffffffu, qz, 2);  // every lane of group g now holds qz of row 8 nb + g
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const float fr = amax > 0.0f ? amax * (1.0f / 32639.0f) : 1.0f, inv = amax > 0.0f ? 32639.0f / amax : 0.0f;  // 32639 keeps the high digit within [-127, 127]
+        f.qz[nb][0] = __shfl_sync(0xffffffffu, qz, 8 * t);      // row 2t   lives in lanes 4 * (2t) ..
+        f.qz[nb][1] = __shfl_sync(0xffffffffu, qz, 8 * t + 4);  // row 2t+1 lives in lanes 4 * (2t+1) ..
+        f.f[nb][0] = __shfl_sync(0xffffffffu, fr, 8 * t) * 0.0625f;
+        f.f[nb][1] = __shfl_sync(0xffffffffu, fr, 8 * t + 4) * 0.0625f;
+        int hi[32], lo[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int qi = __float2int_rn(qs[i] * inv);
+            hi[i] = (qi + 128) >> 8;
+            lo[i] = qi - (hi[i] << 8);
+        }
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+            for (int part = 0; part < 2; ++part)
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {  // b0: local dims 16 kb + 2j + part, b1: +8
+                    const int i0 = 16 * kb + 8 * r + part;
+                    f.b[nb][kb][part][0][r] = (hi[i0] & 255) | ((hi[i0 + 2] & 255) << 8) | ((hi[i0 + 4] & 255) << 16) | ((hi[i0 + 6] & 255) << 24);
+                    f.b[nb][kb][part][1][r] = (lo[i0] & 255) | ((lo[i0 + 2] & 255) << 8) | ((lo[i0 + 4] & 255) << 16) | ((lo[i0 + 6] & 255) << 24);
+                }
+    }
+}
+
 // Scale page of K -> warp scratch in natural dim order.  A page row is 5 halves
 // [scale(2r) scale(2r+1) zp(2r) zp(2r+1) other(r)]; lane l re-packs rows 2l and 2l+1 (20 bytes).
 __device__ __forceinline__ void transpose_k_scale(const uint8_t* kscale_page, uint8_t* scratch, int lane) {
@@ -188,31 +255,35 @@ __device__ __forceinline__ void softmax_block(float (&s)[NB][NG][4], Acc<NB>& ac
 
 // One sealed page (64 keys) of one KV head, staged in shared memory at `pg`.
 template <int NB, bool kOther>
-__device__ __forceinline__ void process_page(const uint8_t* pg, const uint8_t* scratch, const QFrag<NB>& qf, Acc<NB>& acc,
+__device__ __forceinline__ void process_page(const uint8_t* pg, const uint8_t* scratch, const QInt<NB>& qf, Acc<NB>& acc,
                                              int lane, bool need_mask, int first_pos, const int (&row_lim)[NB][2],
                                              int key_begin, int key_end) {
     const int g = lane >> 2, t = lane & 3;
     float s[NB][4][4];
-    // ---- QK: A = codes of keys (g, g+8) of each 16-key group, B = (q' scale_K)^T
+    // ---- QK on the int8 tensor path: A = packed code bytes of keys (g, g+8) masked to their low / high nibbles,
+    //      B = 8-bit digits of (q' scale_K)^T; exact 32-bit accumulation
 #pragma unroll
     for (int grp = 0; grp < 4; ++grp) {
         const uint4 ka = *reinterpret_cast<const uint4*>(pg + kKCodeOff + (grp * 16 + g) * 64 + 16 * t);
-        const uint4 kb = *reinterpret_cast<const uint4*>(pg + kKCodeOff + (grp * 16 + 8 + g) * 64 + 16 * t);
-        const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb.x, kb.y, kb.z, kb.w};
-        float c[NB][4];
+        const uint4 kb8 = *reinterpret_cast<const uint4*>(pg + kKCodeOff + (grp * 16 + 8 + g) * 64 + 16 * t);
+        const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb8.x, kb8.y, kb8.z, kb8.w};
+        int ceh[NB][4], cel[NB][4], coh[NB][4], col[NB][4];
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.0f;
+        for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t ua[4], ub[4];
-            unpack8(wa[i], ua);
-            unpack8(wb[i], ub);
+            for (int e = 0; e < 4; ++e) ceh[nb][e] = cel[nb][e] = coh[nb][e] = col[nb][e] = 0;
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+            const uint32_t l0 = wa[2 * kb] & 0x0F0F0F0Fu, l1 = wb[2 * kb] & 0x0F0F0F0Fu, l2 = wa[2 * kb + 1] & 0x0F0F0F0Fu,
+                           l3 = wb[2 * kb + 1] & 0x0F0F0F0Fu;
+            const uint32_t h0 = wa[2 * kb] & 0xF0F0F0F0u, h1 = wb[2 * kb] & 0xF0F0F0F0u, h2 = wa[2 * kb + 1] & 0xF0F0F0F0u,
+                           h3 = wb[2 * kb + 1] & 0xF0F0F0F0u;
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
-                mma16816(c[nb], ua[0], ub[0], ua[1], ub[1], qf.hi[nb][2 * i][0], qf.hi[nb][2 * i][1]);
-                mma16816(c[nb], ua[2], ub[2], ua[3], ub[3], qf.hi[nb][2 * i + 1][0], qf.hi[nb][2 * i + 1][1]);
-                mma16816(c[nb], ua[0], ub[0], ua[1], ub[1], qf.lo[nb][2 * i][0], qf.lo[nb][2 * i][1]);
-                mma16816(c[nb], ua[2], ub[2], ua[3], ub[3], qf.lo[nb][2 * i + 1][0], qf.lo[nb][2 * i + 1][1]);
+                imma16832(ceh[nb], l0, l1, l2, l3, qf.b[nb][kb][0][0][0], qf.b[nb][kb][0][0][1]);
+                imma16832(cel[nb], l0, l1, l2, l3, qf.b[nb][kb][0][1][0], qf.b[nb][kb][0][1][1]);
+                imma16832(coh[nb], h0, h1, h2, h3, qf.b[nb][kb][1][0][0], qf.b[nb][kb][1][0][1]);
+                imma16832(col[nb], h0, h1, h2, h3, qf.b[nb][kb][1][1][0], qf.b[nb][kb][1][1][1]);
             }
         }
         float o0 = 1.0f, o1 = 1.0f;  // other_K of keys g and g+8 of the group
@@ -222,8 +293,12 @@ __device__ __forceinline__ void process_page(const uint8_t* pg, const uint8_t* s
         }
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-            s[nb][grp][0] = (c[nb][0] + qf.qz[nb][0]) * o0; s[nb][grp][1] = (c[nb][1] + qf.qz[nb][1]) * o0;
-            s[nb][grp][2] = (c[nb][2] + qf.qz[nb][0]) * o1; s[nb][grp][3] = (c[nb][3] + qf.qz[nb][1]) * o1;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                // 16 * sum = 256 (16 even_hi + odd_hi) + (16 even_lo + odd_lo); |.| < 2^31 for 64 code bytes per row
+                const int tot = ((ceh[nb][e] * 16 + coh[nb][e]) << 8) + (cel[nb][e] * 16 + col[nb][e]);
+                s[nb][grp][e] = fmaf(static_cast<float>(tot), qf.f[nb][e & 1], qf.qz[nb][e & 1]) * (e < 2 ? o0 : o1);
+            }
         }
     }
     if (need_mask) {
@@ -417,7 +492,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
         acc.m[nb][0] = acc.m[nb][1] = -INFINITY;
         acc.l[nb][0] = acc.l[nb][1] = acc.z[nb][0] = acc.z[nb][1] = 0.0f;
     }
-    QFrag<NB> qf;
+    QFrag<NB> qf;   // fp16 fragments for the open tile (stage rows)
+    QInt<NB> qi;    // 8-bit digits for the quantised pages
     bool timed_out = false;
 
     if (split < P.nsplit) {
@@ -460,7 +536,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
                     __syncwarp();
                     transpose_k_scale(pg + kKScaleOff, scratch, lane);
                     __syncwarp();
-                    build_qfrag<true, NB>(sm, scratch, lane, qf);
+                    build_qint<NB>(sm, scratch, lane, qi);
                 } else if constexpr (kOther) {
                     __syncwarp();
                     transpose_k_scale(pg + kKScaleOff, scratch, lane);
@@ -468,7 +544,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
                 }
                 const int first = lp * kPage;
                 const bool need_mask = first + kPage - 1 > min_lim || first < key_begin || first + kPage > key_end;
-                process_page<NB, kOther>(pg, scratch, qf, acc, lane, need_mask, first, row_lim, key_begin, key_end);
+                process_page<NB, kOther>(pg, scratch, qi, acc, lane, need_mask, first, row_lim, key_begin, key_end);
             }
             // refill this slot with the page after next; the generic-proxy reads above must be ordered first
             __syncwarp();
