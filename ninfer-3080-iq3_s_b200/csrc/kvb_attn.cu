@@ -701,30 +701,34 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
 
 // Cross-GPU (or cross-range) merge of exported partials: parts_m in natural-log units.
 // Part p keeps its m and l at [p * ml_stride + row] and its o at [p * o_stride + row * D].
+template <int DD>
 __global__ void __launch_bounds__(128) merge_kernel(const float* __restrict__ pm, const float* __restrict__ pl,
                                                     const float* __restrict__ po, int parts, int rows, int64_t ml_stride,
                                                     int64_t o_stride, int dtype, uint16_t* __restrict__ out) {
+    constexpr int R = DD / 32;
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
     float m = -INFINITY;
     for (int p = 0; p < parts; ++p) m = fmaxf(m, pm[p * ml_stride + row]);
-    float l = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float l = 0.0f, o[R];
+#pragma unroll
+    for (int j = 0; j < R; ++j) o[j] = 0.0f;
     if (m != -INFINITY) {
         for (int p = 0; p < parts; ++p) {
             const int64_t i = p * ml_stride + row;
             const float w = __expf(pm[i] - m);
             l += w * pl[i];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o[j] += w * po[p * o_stride + static_cast<int64_t>(row) * D + lane + 32 * j];
+            for (int j = 0; j < R; ++j) o[j] += w * po[p * o_stride + static_cast<int64_t>(row) * DD + lane + 32 * j];
         }
     }
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o[j] *= inv;
-    hadamard_warp<D>(o, lane);
+    for (int j = 0; j < R; ++j) o[j] *= inv;
+    hadamard_warp<DD>(o, lane);
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-        out[static_cast<int64_t>(row) * D + lane + 32 * j] = dtype == KVB_DTYPE_BF16 ? f32_to_out<true>(o[j]) : f32_to_out<false>(o[j]);
+    for (int j = 0; j < R; ++j)
+        out[static_cast<int64_t>(row) * DD + lane + 32 * j] = dtype == KVB_DTYPE_BF16 ? f32_to_out<true>(o[j]) : f32_to_out<false>(o[j]);
 }
 
 int g_sm_count = 0;
@@ -759,6 +763,14 @@ int split_count(int kv_len_max, int kv_heads, int zblocks) {
 namespace kvb {
 namespace {
 
+}  // namespace
+// kvb_attn_general.cu: head_dim 256 and caches written with Sinkhorn iterations > 0
+size_t general_workspace_bytes(int kv_len_max, int q_heads, int head_dim, int rows);
+int launch_general_attention(const kvb_layer* layer, const void* q, const int32_t* pos_dev, const int32_t* total_pos_dev, int T,
+                             float scale, int kv_len_max, int key_begin, int key_end, void* workspace, void* out, float* part_m,
+                             float* part_l, float* part_o, cudaStream_t stream);
+namespace {
+
 int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_dev, const int32_t* total_pos_dev, int T,
                      float scale, int kv_len_max,
                      int key_begin, int key_end, void* workspace, void* out, float* part_m, float* part_l,
@@ -768,10 +780,10 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     if (out == nullptr && part_m == nullptr) return fail(KVB_EINVAL, "%s: null output", who);
     if (T < 1 || T > 8) return fail(KVB_ERANGE, "%s: %d query tokens (1..8 supported)", who, T);
     if (kv_len_max < 1) return fail(KVB_EINVAL, "%s: kv_len_max %d", who, kv_len_max);
-    if (layer->head_dim != 128) return fail(KVB_ERANGE, "%s: head_dim %d (the fused attention kernels cover 128)", who, layer->head_dim);
-    if (layer->sinkhorn_iters != 0)
-        return fail(KVB_ERANGE, "%s: sinkhorn_iters %d (the fused attention kernels cover the iters = 0 cache)", who, layer->sinkhorn_iters);
     if (layer->stage == nullptr) return fail(KVB_EINVAL, "%s: layer has no stage buffer", who);
+    if (layer->head_dim != 128 || layer->sinkhorn_iters != 0)  // shapes outside the tuned kernels: general kernel, same semantics
+        return launch_general_attention(layer, q, pos_dev, total_pos_dev, T, scale, kv_len_max, key_begin, key_end, workspace, out,
+                                        part_m, part_l, part_o, stream);
     const int Z = zblocks_of(layer->q_heads, layer->kv_heads, T);
     const int nsplit = split_count(kv_len_max, layer->kv_heads, Z);
     const int parts = nsplit + 1;
@@ -824,6 +836,8 @@ extern "C" size_t kvb_workspace_bytes(int kv_len_max, int kv_heads, int q_heads,
     const int Z = kvb::zblocks_of(q_heads, kv_heads, rows);
     const size_t parts = kvb::split_count(kv_len_max, kv_heads, Z) + 1;
     size_t bytes = static_cast<size_t>(kv_heads) * Z * parts * kvb::kRows * (head_dim + 2) * sizeof(float);
+    const size_t general = kvb::general_workspace_bytes(kv_len_max, q_heads, head_dim, rows);
+    if (general > bytes) bytes = general;
     if (rows * (q_heads / kv_heads) >= kDenseRows) {  // verify steps this wide run on the chunk-attention kernel
         const size_t dense = kvb_prefill_workspace_bytes(kv_len_max, kv_heads, q_heads, head_dim, rows);
         if (dense > bytes) bytes = dense;
@@ -852,10 +866,15 @@ extern "C" int kvb_merge_partials(const float* parts_m, const float* parts_l, co
     if (parts_m == nullptr || parts_l == nullptr || parts_o == nullptr || out == nullptr)
         return fail(KVB_EINVAL, "kvb_merge_partials: null argument");
     if (parts < 1 || q_heads < 1) return fail(KVB_EINVAL, "kvb_merge_partials: parts %d / q_heads %d", parts, q_heads);
-    if (head_dim != 128) return fail(KVB_ERANGE, "kvb_merge_partials: head_dim %d (128 supported)", head_dim);
-    merge_kernel<<<(q_heads + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(parts_m, parts_l, parts_o, parts, q_heads, q_heads,
-                                                                                  static_cast<int64_t>(q_heads) * D, dtype,
-                                                                                  static_cast<uint16_t*>(out));
+    if (head_dim != 128 && head_dim != 256) return fail(KVB_ERANGE, "kvb_merge_partials: head_dim %d (128 or 256)", head_dim);
+    const dim3 grid((q_heads + 3) / 4);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (head_dim == 128)
+        merge_kernel<128><<<grid, 128, 0, st>>>(parts_m, parts_l, parts_o, parts, q_heads, q_heads, static_cast<int64_t>(q_heads) * 128, dtype,
+                                                static_cast<uint16_t*>(out));
+    else
+        merge_kernel<256><<<grid, 128, 0, st>>>(parts_m, parts_l, parts_o, parts, q_heads, q_heads, static_cast<int64_t>(q_heads) * 256, dtype,
+                                                static_cast<uint16_t*>(out));
     KVB_CUDA_OK(cudaGetLastError());
     return KVB_OK;
 }
@@ -865,11 +884,16 @@ extern "C" int kvb_merge_partials_packed(const float* packed, int parts, int q_h
     using namespace kvb;
     if (packed == nullptr || out == nullptr) return fail(KVB_EINVAL, "kvb_merge_partials_packed: null argument");
     if (parts < 1 || q_heads < 1) return fail(KVB_EINVAL, "kvb_merge_partials_packed: parts %d / q_heads %d", parts, q_heads);
-    if (head_dim != 128) return fail(KVB_ERANGE, "kvb_merge_partials_packed: head_dim %d (128 supported)", head_dim);
-    const int64_t block = static_cast<int64_t>(q_heads) * (D + 2);
-    merge_kernel<<<(q_heads + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(packed, packed + q_heads, packed + 2 * q_heads, parts,
-                                                                                  q_heads, block, block, dtype,
-                                                                                  static_cast<uint16_t*>(out));
+    if (head_dim != 128 && head_dim != 256) return fail(KVB_ERANGE, "kvb_merge_partials_packed: head_dim %d (128 or 256)", head_dim);
+    const int64_t block = static_cast<int64_t>(q_heads) * (head_dim + 2);
+    const dim3 grid((q_heads + 3) / 4);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (head_dim == 128)
+        merge_kernel<128><<<grid, 128, 0, st>>>(packed, packed + q_heads, packed + 2 * q_heads, parts, q_heads, block, block, dtype,
+                                                static_cast<uint16_t*>(out));
+    else
+        merge_kernel<256><<<grid, 128, 0, st>>>(packed, packed + q_heads, packed + 2 * q_heads, parts, q_heads, block, block, dtype,
+                                                static_cast<uint16_t*>(out));
     KVB_CUDA_OK(cudaGetLastError());
     return KVB_OK;
 }

@@ -409,11 +409,21 @@ void prefill_shape(int kv_len_max, int kv_heads, int q_heads, int tokens, int* m
 }  // namespace
 }  // namespace kvb
 
+namespace kvb {
+// kvb_attn_general.cu: head_dim 256 and caches written with Sinkhorn iterations > 0
+size_t general_workspace_bytes(int kv_len_max, int q_heads, int head_dim, int rows);
+int launch_general_attention(const kvb_layer* layer, const void* q, const int32_t* pos_dev, const int32_t* total_pos_dev, int T,
+                             float scale, int kv_len_max, int key_begin, int key_end, void* workspace, void* out, float* part_m,
+                             float* part_l, float* part_o, cudaStream_t stream);
+}  // namespace kvb
+
 extern "C" size_t kvb_prefill_workspace_bytes(int kv_len_max, int kv_heads, int q_heads, int head_dim, int tokens) {
     if (kv_heads < 1 || q_heads < kv_heads || tokens < 1) return 0;
     int mtiles, ksplit;
     kvb::prefill_shape(kv_len_max, kv_heads, q_heads, tokens, &mtiles, &ksplit);
-    return static_cast<size_t>(kv_heads) * mtiles * ksplit * kvb::kM * (head_dim + 2) * sizeof(float);
+    const size_t tuned = static_cast<size_t>(kv_heads) * mtiles * ksplit * kvb::kM * (head_dim + 2) * sizeof(float);
+    const size_t general = kvb::general_workspace_bytes(kv_len_max, q_heads, head_dim, tokens);  // head_dim 256, Sinkhorn caches
+    return tuned > general ? tuned : general;
 }
 
 namespace kvb {
@@ -455,9 +465,11 @@ extern "C" int kvb_attn_prefill(const kvb_layer* layer, const void* q, const voi
     if (int st = check_layer(layer, "kvb_attn_prefill")) return st;
     if (tokens < 1) return fail(KVB_EINVAL, "kvb_attn_prefill: tokens = %d", tokens);
     if (q == nullptr || workspace == nullptr || out == nullptr) return fail(KVB_EINVAL, "kvb_attn_prefill: null q / workspace / out");
-    if (layer->head_dim != 128) return fail(KVB_ERANGE, "kvb_attn_prefill: head_dim %d (the fused attention kernels cover 128)", layer->head_dim);
-    if (layer->sinkhorn_iters != 0)
-        return fail(KVB_ERANGE, "kvb_attn_prefill: sinkhorn_iters %d (the fused attention kernels cover the iters = 0 cache)", layer->sinkhorn_iters);
+    if (layer->stage == nullptr) return fail(KVB_EINVAL, "kvb_attn_prefill: layer has no stage buffer");
+    if (tokens > 65535) return fail(KVB_ERANGE, "kvb_attn_prefill: %d tokens in one chunk (at most 65535)", tokens);
     if (int st = kvb_append(layer, k, v, positions_dev, tokens, stream)) return st;
+    if (layer->head_dim != 128 || layer->sinkhorn_iters != 0)  // shapes outside the tensor-core kernel: general kernel, same semantics
+        return launch_general_attention(layer, q, positions_dev, positions_dev + (tokens - 1), tokens, scale, kv_len_max, 0, INT_MAX,
+                                        workspace, out, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
     return launch_chunk_attention(layer, q, positions_dev, tokens, scale, kv_len_max, workspace, out, static_cast<cudaStream_t>(stream));
 }

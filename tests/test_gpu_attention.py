@@ -194,3 +194,52 @@ def test_packed_partial_and_merge():
     full = tw.gpu.attn_decode(qd, pos, scale, T)
     torch.cuda.synchronize()
     assert torch.equal(out, full)
+
+
+def _sync_cpu_from_gpu(tw):
+    """Make the oracle layer hold exactly the bytes the GPU layer holds (needed when the two quantisers may
+    differ in a few codes, i.e. with Sinkhorn iterations > 0)."""
+    g, c = tw.gpu, tw.cpu
+    c.k_code[:] = g.k_code.cpu().numpy(); c.v_code[:] = g.v_code.cpu().numpy()
+    c.k_scale[:] = g.k_scale.cpu().numpy().view(np.uint16); c.v_scale[:] = g.v_scale.cpu().numpy().view(np.uint16)
+    c.stage[:] = g.stage.cpu().numpy().view(np.uint16).reshape(c.stage.shape)
+
+
+@pytest.mark.parametrize("D,H,QH,iters,T", [(256, 4, 24, 0, 700), (256, 2, 4, 0, 333), (128, 4, 24, 16, 600), (256, 2, 8, 16, 300)])
+def test_general_kernel_head_dim_256_and_sinkhorn(D, H, QH, iters, T):
+    """The reference engine's own geometry (head_dim 256, 16 Sinkhorn iterations) runs on the general kernel:
+    decode, a 4-row verify step and a small prefill chunk, against the oracle on the same cache bytes."""
+    import torch
+
+    tw = Twin(D=D, H=H, QH=QH, capacity_tokens=T + 40, seed=101, iters=iters)
+    k, v = orc.synth_kv(102, T + 40, H, D, 1), orc.synth_kv(102, T + 40, H, D, 2)
+    tw.append(k[:T], v[:T])
+    _sync_cpu_from_gpu(tw)
+    scale = 1.0 / np.sqrt(D)
+    q = orc.synth_q(102, 1, QH, D)
+    want = tw.cpu.attention(q, [T - 1], scale, QH, threads=4)
+    ok, msg = attn_close(_decode(tw, q[0], T - 1), want[0])
+    assert ok, "decode: " + msg
+    # verify step of 4 rows (append inside)
+    q4 = orc.synth_q(103, 4, QH, D)
+    pos = np.arange(T, T + 4, dtype=np.int32)
+    out = tw.gpu.attn_verify(torch.from_numpy(q4).to(tw.dev), torch.from_numpy(k[T:T + 4]).to(tw.dev), torch.from_numpy(v[T:T + 4]).to(tw.dev),
+                             torch.from_numpy(pos).to(tw.dev), scale, T + 40)
+    torch.cuda.synchronize()
+    tw.cpu.append(k[T:T + 4], v[T:T + 4], T)
+    _sync_cpu_from_gpu(tw)
+    want = tw.cpu.attention(q4, pos, scale, QH, threads=4)
+    ok, msg = attn_close(out.float().cpu().numpy(), want)
+    assert ok, "verify: " + msg
+    # prefill chunk of 36 rows
+    qc = orc.synth_q(104, 36, QH, D)
+    pos = np.arange(T + 4, T + 40, dtype=np.int32)
+    out = tw.gpu.attn_prefill(torch.from_numpy(qc).to(tw.dev), torch.from_numpy(k[T + 4:]).to(tw.dev), torch.from_numpy(v[T + 4:]).to(tw.dev),
+                              torch.from_numpy(pos).to(tw.dev), scale, T + 40)
+    torch.cuda.synchronize()
+    tw.cpu.append(k[T + 4:], v[T + 4:], T + 4)
+    _sync_cpu_from_gpu(tw)
+    want = tw.cpu.attention(qc, pos, scale, QH, threads=4)
+    ok, msg = attn_close(out.float().cpu().numpy(), want)
+    assert ok, "prefill: " + msg
+    assert tw.gpu.errors() == 0
