@@ -139,6 +139,30 @@ int kvb_merge_partials(const float* parts_m, const float* parts_l, const float* 
  * part_m, part_l, part_o point into one send buffer.  No counterpart in the reference (single GPU). */
 int kvb_merge_partials_packed(const float* packed, int parts, int q_heads, int head_dim, int dtype, void* out, void* stream);
 
+/* Sequence-range sharded decode without a collective library on the data path.  No counterpart in the reference
+ * (single GPU).  Every rank holds its tile range of the sequence as a local cache and owns a ring buffer of
+ * kvb_peer_ring_bytes() bytes that all ranks can write (peer memory over NVLink, e.g. a symmetric-memory
+ * allocation); `peer_bufs_dev` is a device array with the ring buffer address of every rank in rank order, this
+ * rank's own included.  One call = attention over the local range, then one kernel in which the CTA of each query
+ * row stores its (m, l, o) partial of the row straight into every peer's ring buffer -- each fp32 value in one
+ * 8-byte word together with the call number, so a word that shows the expected call number also shows its value
+ * and no fence or flag is needed -- waits, bounded by `max_spins` polls per word (0 = default), for the peers'
+ * partials of the same row, merges, rotates back and writes `out`: two launches, like the single-GPU decode.
+ * A wait that runs out sets KVB_ERR_WAIT_TIMEOUT in *layer->error_word and writes zeros; nothing traps or hangs.
+ * `state` is three zero-initialised device words owned by this rank.  Ring buffer and state must be zeroed once
+ * before the first call; all ranks must make the same sequence of calls on a ring; calls on one ring must not
+ * overlap on the GPU.  head_dim 128, sinkhorn_iters 0, at most 16 ranks. */
+typedef struct kvb_peer_ring {
+    void* const* peer_bufs_dev;
+    void* local_buf;
+    uint32_t* state;
+    int32_t rank, world;
+    uint32_t max_spins;
+} kvb_peer_ring;
+size_t kvb_peer_ring_bytes(int world, int q_heads, int head_dim);
+int kvb_attn_decode_sharded(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
+                            void* workspace, const kvb_peer_ring* ring, void* out, void* stream);
+
 /* MTP verify: append `width` (1..8) new rows, then causal attention of those rows (row i sees keys
  * 0..positions[i]).  q, out: [width][q_heads][head_dim]; k, v: [width][kv_heads][head_dim].
  * Replaces causal_attention_small_t_launch (P3:3508-3610). */

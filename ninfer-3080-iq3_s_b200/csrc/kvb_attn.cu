@@ -631,11 +631,40 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
 // w, w+8, ... and issues all its loads before using any (the kernel is pure load latency), lane l owns
 // dims 4l..4l+3; the eight warp sums meet in shared memory and warp 0 finishes the row.
 constexpr int kReduceWarps = 8, kMaxPartsPerWarp = 8;  // up to 64 parts
+// Where a sharded decode sends its partial: the ring buffers of all ranks (peer memory over NVLink; this rank's
+// own buffer included), see kvb_peer_ring in the header.  A ring buffer holds [slot = call & 1][sender] blocks of
+// m[rows] | l[rows] | o[rows][D]; every fp32 value travels in one aligned 8-byte word together with the number
+// of the call that produced it (value in the low half, call number in the high half).  An 8-byte store arrives
+// whole, so a reader that sees the expected call number in a word also sees its value: no fences, no separate
+// flags, the latency of the exchange is one store across NVLink.
+constexpr int kRingMaxWorld = 16;
+struct PushTarget {
+    unsigned long long* const* peer_bufs;  // device array of `world` pointers, or null: no push
+    uint32_t* state;                       // local words: [0] calls completed, [2] CTAs of this call that are done
+    const unsigned long long* local_buf;   // this rank's own ring buffer (what the peers write)
+    uint32_t max_spins;                    // bound of the wait for a peer's word
+    uint32_t* error_word;
+    int rank, world;
+};
+__device__ __forceinline__ void ring_store(unsigned long long* p, float v, uint32_t call) {
+    *reinterpret_cast<volatile unsigned long long*>(p) = (static_cast<unsigned long long>(call) << 32) | __float_as_uint(v);
+}
+
+__device__ __forceinline__ bool ring_load(const unsigned long long* p, uint32_t call, uint32_t max_spins, float& v) {
+    for (uint32_t i = 0; i < max_spins; ++i) {
+        const unsigned long long w = *reinterpret_cast<const volatile unsigned long long*>(p);
+        if (static_cast<uint32_t>(w >> 32) == call) { v = __uint_as_float(static_cast<uint32_t>(w)); return true; }
+        __nanosleep(32);
+    }
+    v = 0.0f;
+    return false;
+}
+
 __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
                                                                   const float* __restrict__ ws_o, int parts, int T, int q_heads,
                                                                   int kv_heads, int zblocks, int dtype, uint16_t* __restrict__ out,
                                                                   float* __restrict__ part_m, float* __restrict__ part_l,
-                                                                  float* __restrict__ part_o) {
+                                                                  float* __restrict__ part_o, const PushTarget push) {
     __shared__ float4 so[kReduceWarps][32];
     __shared__ float sl[kReduceWarps];
     const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -679,6 +708,63 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
         const float4 x = so[w][lane];
         acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
         l += sl[w];
+    }
+    if (push.peer_bufs != nullptr) {
+        // Sharded decode: this CTA owns one query row on every rank.  It stores its partial of the row straight into
+        // every peer's ring buffer, waits (bounded) for the peers' partials of the same row in its own ring buffer,
+        // merges them with its own, normalises, rotates back and stores -- send, receive and merge in one kernel.
+        const uint32_t call = *reinterpret_cast<volatile uint32_t*>(push.state) + 1u, slot = call & 1u;
+        const int rows = T * q_heads;
+        const int64_t block = static_cast<int64_t>(rows) * (D + 2);
+        const float mine = m * kLn2;  // natural-log units, like every exported partial
+        for (int p = 0; p < push.world; ++p) {
+            if (p == push.rank) continue;
+            unsigned long long* dst = push.peer_bufs[p] + (static_cast<int64_t>(slot) * push.world + push.rank) * block;
+            if (lane == 0) { ring_store(dst + row, mine, call); ring_store(dst + rows + row, l, call); }
+            unsigned long long* o = dst + 2 * rows + static_cast<int64_t>(row) * D + 4 * lane;
+            ring_store(o, acc.x, call); ring_store(o + 1, acc.y, call); ring_store(o + 2, acc.z, call); ring_store(o + 3, acc.w, call);
+        }
+        bool ok = true;
+        float pm[kRingMaxWorld], gm = mine;
+        for (int p = 0; p < push.world; ++p) {
+            pm[p] = mine;
+            if (p == push.rank) continue;
+            ok &= ring_load(push.local_buf + (static_cast<int64_t>(slot) * push.world + p) * block + row, call, push.max_spins, pm[p]);
+            gm = fmaxf(gm, pm[p]);
+        }
+        const float w0 = gm == -INFINITY ? 0.0f : __expf(mine - gm);
+        float gl = w0 * l;
+        float4 go = make_float4(w0 * acc.x, w0 * acc.y, w0 * acc.z, w0 * acc.w);
+        for (int p = 0; p < push.world; ++p) {
+            if (p == push.rank) continue;
+            const unsigned long long* blk = push.local_buf + (static_cast<int64_t>(slot) * push.world + p) * block;
+            float pl, v[4];
+            ok &= ring_load(blk + rows + row, call, push.max_spins, pl);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ok &= ring_load(blk + 2 * rows + static_cast<int64_t>(row) * D + 4 * lane + j, call, push.max_spins, v[j]);
+            const float w = gm == -INFINITY ? 0.0f : __expf(pm[p] - gm);
+            gl += w * pl;
+            go.x += w * v[0]; go.y += w * v[1]; go.z += w * v[2]; go.w += w * v[3];
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok && lane == 0 && push.error_word != nullptr) atomicOr(push.error_word, KVB_ERR_WAIT_TIMEOUT);
+        const float ginv = ok && gl > 0.0f ? 1.0f / gl : 0.0f;  // a wait that ran out: zeros, not a half-merged row
+        so[0][lane] = make_float4(go.x * ginv, go.y * ginv, go.z * ginv, go.w * ginv);
+        __syncwarp();
+        const float* gflat = reinterpret_cast<const float*>(so[0]);
+        float o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = gflat[lane + 32 * j];
+        hadamard_warp<D>(o, lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            out[static_cast<int64_t>(row) * D + lane + 32 * j] = dtype == KVB_DTYPE_BF16 ? f32_to_out<true>(o[j]) : f32_to_out<false>(o[j]);
+        if (lane == 0 && atomicAdd(&push.state[2], 1u) == gridDim.x - 1) {  // every CTA of this call has read the call number
+            push.state[2] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t*>(push.state) = call;
+        }
+        return;
     }
     if (part_m != nullptr) {
         if (lane == 0) { part_m[row] = m * kLn2; part_l[row] = l; }
@@ -774,13 +860,15 @@ namespace {
 int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_dev, const int32_t* total_pos_dev, int T,
                      float scale, int kv_len_max,
                      int key_begin, int key_end, void* workspace, void* out, float* part_m, float* part_l,
-                     float* part_o, cudaStream_t stream, const char* who) {
+                     float* part_o, cudaStream_t stream, const char* who, const PushTarget* push = nullptr) {
     if (int st = check_layer(layer, who)) return st;
     if (q == nullptr || pos_dev == nullptr || workspace == nullptr) return fail(KVB_EINVAL, "%s: null q / positions / workspace", who);
-    if (out == nullptr && part_m == nullptr) return fail(KVB_EINVAL, "%s: null output", who);
+    if (out == nullptr && part_m == nullptr && push == nullptr) return fail(KVB_EINVAL, "%s: null output", who);
     if (T < 1 || T > 8) return fail(KVB_ERANGE, "%s: %d query tokens (1..8 supported)", who, T);
     if (kv_len_max < 1) return fail(KVB_EINVAL, "%s: kv_len_max %d", who, kv_len_max);
     if (layer->stage == nullptr) return fail(KVB_EINVAL, "%s: layer has no stage buffer", who);
+    if ((layer->head_dim != 128 || layer->sinkhorn_iters != 0) && push != nullptr)
+        return fail(KVB_ERANGE, "%s: the sharded decode covers head_dim 128 caches written with sinkhorn_iters = 0", who);
     if (layer->head_dim != 128 || layer->sinkhorn_iters != 0)  // shapes outside the tuned kernels: general kernel, same semantics
         return launch_general_attention(layer, q, pos_dev, total_pos_dev, T, scale, kv_len_max, key_begin, key_end, workspace, out,
                                         part_m, part_l, part_o, stream);
@@ -815,7 +903,8 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     KVB_CUDA_OK(cudaGetLastError());
     const int total_rows = T * layer->q_heads;
     reduce_kernel<<<total_rows, kReduceWarps * 32, 0, stream>>>(P.ws_m, P.ws_l, P.ws_o, parts, T, layer->q_heads, layer->kv_heads, Z,
-                                                            layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o);
+                                                            layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o,
+                                                            push != nullptr ? *push : PushTarget{nullptr, nullptr, nullptr, 0u, nullptr, 0, 0});
     KVB_CUDA_OK(cudaGetLastError());
     return KVB_OK;
 }
@@ -896,6 +985,25 @@ extern "C" int kvb_merge_partials_packed(const float* packed, int parts, int q_h
                                                 static_cast<uint16_t*>(out));
     KVB_CUDA_OK(cudaGetLastError());
     return KVB_OK;
+}
+
+extern "C" size_t kvb_peer_ring_bytes(int world, int q_heads, int head_dim) {
+    if (world < 1 || world > kvb::kRingMaxWorld || q_heads < 1) return 0;
+    return static_cast<size_t>(2) * world * q_heads * (head_dim + 2) * sizeof(unsigned long long);  // two slots, 8 bytes per value
+}
+
+extern "C" int kvb_attn_decode_sharded(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
+                                       void* workspace, const kvb_peer_ring* ring, void* out, void* stream) {
+    using namespace kvb;
+    if (ring == nullptr || ring->peer_bufs_dev == nullptr || ring->local_buf == nullptr || ring->state == nullptr || out == nullptr)
+        return fail(KVB_EINVAL, "kvb_attn_decode_sharded: null ring / buffers / out");
+    if (ring->world < 1 || ring->world > kRingMaxWorld || ring->rank < 0 || ring->rank >= ring->world)
+        return fail(KVB_EINVAL, "kvb_attn_decode_sharded: rank %d of world %d (1..%d ranks)", ring->rank, ring->world, kRingMaxWorld);
+    const PushTarget push{reinterpret_cast<unsigned long long* const*>(ring->peer_bufs_dev), ring->state,
+                          static_cast<const unsigned long long*>(ring->local_buf), ring->max_spins ? ring->max_spins : (1u << 22),
+                          layer->error_word, ring->rank, ring->world};
+    return launch_attention(layer, q, pos_dev, pos_dev, 1, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr, nullptr,
+                            static_cast<cudaStream_t>(stream), "kvb_attn_decode_sharded", &push);
 }
 
 namespace kvb {

@@ -87,3 +87,72 @@ class ShardedDecode:
         self.layer.attn_decode_partial_packed(q, local_pos, scale, local_len_max, self.send)
         dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
         return cache.merge_partials_packed(self.recv, self.world, self.layer.q_heads, self.layer.head_dim, out)
+
+
+class PeerRing:
+    """Ring buffers for kvb_attn_decode_sharded: one buffer per rank that every rank can write (peer memory).
+    `PeerRing.symmetric(...)` allocates it with torch's symmetric memory over the process group (NVLink peer
+    mappings); `PeerRing.loopback(...)` builds a single-process stand-in whose "peers" are local buffers (tests)."""
+
+    def __init__(self, local_buf, peer_ptrs, rank: int, world: int, device, max_spins: int = 0, keep=()):
+        import ctypes as C
+
+        import torch
+
+        from . import capi
+
+        self.local_buf, self.rank, self.world, self._keep = local_buf, rank, world, keep
+        self.peer_ptrs = torch.tensor(list(peer_ptrs), dtype=torch.int64, device=device)
+        self.state = torch.zeros(4, dtype=torch.int32, device=device)
+        self.c = capi.kvb_peer_ring(peer_bufs_dev=self.peer_ptrs.data_ptr(), local_buf=local_buf.data_ptr(),
+                                    state=self.state.data_ptr(), rank=rank, world=world, max_spins=max_spins)
+        self._C = C
+
+    @staticmethod
+    def nbytes(world: int, q_heads: int, head_dim: int) -> int:
+        from . import capi
+
+        return capi.load().kvb_peer_ring_bytes(world, q_heads, head_dim)
+
+    @classmethod
+    def symmetric(cls, q_heads: int, head_dim: int, device, group=None, max_spins: int = 0):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group or dist.group.WORLD
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        buf = symm_mem.empty(cls.nbytes(world, q_heads, head_dim) // 4, dtype=torch.float32, device=device)
+        buf.zero_()
+        hdl = symm_mem.rendezvous(buf, group)
+        torch.cuda.synchronize()
+        dist.barrier(group)  # every rank's buffer is zeroed before anybody may push
+        return cls(buf, [int(p) for p in hdl.buffer_ptrs], rank, world, device, max_spins, keep=(hdl,))
+
+    @classmethod
+    def loopback(cls, q_heads: int, head_dim: int, device, world: int = 1, rank: int = 0, max_spins: int = 0):
+        import torch
+
+        bufs = [torch.zeros(cls.nbytes(world, q_heads, head_dim) // 4, dtype=torch.float32, device=device) for _ in range(world)]
+        return cls(bufs[rank], [b.data_ptr() for b in bufs], rank, world, device, max_spins, keep=tuple(bufs))
+
+
+class RingShardedDecode:
+    """Range-sharded decode with the partial exchange done by the kernels themselves (peer stores + arrival flags)."""
+
+    def __init__(self, layer, ring: PeerRing):
+        self.layer, self.ring = layer, ring
+
+    def attn_decode(self, q, local_pos, scale: float, local_len_max: int, out):
+        import ctypes as C
+
+        import torch
+
+        from . import capi
+
+        L = self.layer
+        capi.check(capi.load().kvb_attn_decode_sharded(C.byref(L.c), C.c_void_p(q.data_ptr()), C.c_void_p(local_pos.data_ptr()), scale,
+                                                       local_len_max, C.c_void_p(L.workspace(local_len_max, 1).data_ptr()),
+                                                       C.byref(self.ring.c), C.c_void_p(out.data_ptr()),
+                                                       C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out

@@ -243,3 +243,38 @@ def test_general_kernel_head_dim_256_and_sinkhorn(D, H, QH, iters, T):
     ok, msg = attn_close(out.float().cpu().numpy(), want)
     assert ok, "prefill: " + msg
     assert tw.gpu.errors() == 0
+
+
+def test_sharded_decode_ring_loopback_and_bounded_wait():
+    """kvb_attn_decode_sharded on one GPU: with a one-rank ring the result equals kvb_attn_decode on every call (both
+    ring slots, advancing call numbers); with a second rank that never sends, the bounded wait runs out, the error
+    word reports it, zeros are written and the next call still works -- nothing hangs."""
+    import torch
+
+    capi = pkg().capi
+    sh = pkg().sharded
+    T = 1100
+    tw = Twin(D=128, H=4, QH=24, capacity_tokens=T, seed=111)
+    k, v = orc.synth_kv(112, T, 4, 128, 1), orc.synth_kv(112, T, 4, 128, 2)
+    tw.append(k, v)
+    pos = torch.tensor([T - 1], dtype=torch.int32, device=tw.dev)
+    scale = 1.0 / np.sqrt(128)
+    ring = sh.PeerRing.loopback(24, 128, tw.dev)
+    dec = sh.RingShardedDecode(tw.gpu, ring)
+    for call in range(5):
+        qd = torch.from_numpy(orc.synth_q(113 + call, 1, 24, 128)[0]).to(tw.dev)
+        out = torch.empty_like(qd)
+        dec.attn_decode(qd, pos, scale, T, out)
+        ref = tw.gpu.attn_decode(qd, pos, scale, T)
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref), call
+    assert int(ring.state[0].item()) == 5 and tw.gpu.errors() == 0
+    # a rank that never arrives: the wait is bounded
+    ring2 = sh.PeerRing.loopback(24, 128, tw.dev, world=2, rank=0, max_spins=2000)
+    dec2 = sh.RingShardedDecode(tw.gpu, ring2)
+    out = torch.full((24, 128), 7.0, dtype=torch.float16, device=tw.dev)
+    dec2.attn_decode(qd, pos, scale, T, out)
+    torch.cuda.synchronize()
+    assert tw.gpu.errors() & capi.ERR_WAIT_TIMEOUT
+    assert not out.any()
+    assert int(ring2.state[0].item()) == 1
