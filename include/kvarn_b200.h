@@ -142,18 +142,19 @@ int kvb_merge_partials_packed(const float* packed, int parts, int q_heads, int h
 /* Sequence-range sharded decode without a collective library on the data path.  No counterpart in the reference
  * (single GPU).  Every rank holds its tile range of the sequence as a local cache and owns a ring buffer of
  * kvb_peer_ring_bytes() bytes that all ranks can write (peer memory over NVLink, e.g. a symmetric-memory
- * allocation); `peer_bufs_dev` is a device array with the ring buffer address of every rank in rank order, this
- * rank's own included.  One call = attention over the local range, then one kernel in which the CTA of each query
+ * allocation); `peer_bufs` is a host array with the ring buffer address (16-byte aligned) of every rank in rank
+ * order, this rank's own included; it is read during the call only.  One call = attention over the local range, then one kernel in which the CTA of each query
  * row stores its (m, l, o) partial of the row straight into every peer's ring buffer -- each fp32 value in one
  * 8-byte word together with the call number, so a word that shows the expected call number also shows its value
- * and no fence or flag is needed -- waits, bounded by `max_spins` polls per word (0 = default), for the peers'
- * partials of the same row, merges, rotates back and writes `out`: two launches, like the single-GPU decode.
+ * and no fence or flag is needed -- waits, bounded by `max_spins` polling rounds (0 = default), for the peers'
+ * partials of the same row, merges them in rank order (all ranks write the same bits), rotates back and writes
+ * `out`: two launches, like the single-GPU decode.
  * A wait that runs out sets KVB_ERR_WAIT_TIMEOUT in *layer->error_word and writes zeros; nothing traps or hangs.
  * `state` is three zero-initialised device words owned by this rank.  Ring buffer and state must be zeroed once
  * before the first call; all ranks must make the same sequence of calls on a ring; calls on one ring must not
  * overlap on the GPU.  head_dim 128, sinkhorn_iters 0, at most 16 ranks. */
 typedef struct kvb_peer_ring {
-    void* const* peer_bufs_dev;
+    void* const* peer_bufs;
     void* local_buf;
     uint32_t* state;
     int32_t rank, world;

@@ -33,7 +33,7 @@ class kvb_layer(C.Structure):
 
 
 class kvb_peer_ring(C.Structure):
-    _fields_ = [("peer_bufs_dev", C.c_void_p), ("local_buf", C.c_void_p), ("state", C.c_void_p), ("rank", C.c_int32),
+    _fields_ = [("peer_bufs", C.POINTER(C.c_void_p)), ("local_buf", C.c_void_p), ("state", C.c_void_p), ("rank", C.c_int32),
                 ("world", C.c_int32), ("max_spins", C.c_uint32)]
 
 

@@ -633,32 +633,31 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
 constexpr int kReduceWarps = 8, kMaxPartsPerWarp = 8;  // up to 64 parts
 // Where a sharded decode sends its partial: the ring buffers of all ranks (peer memory over NVLink; this rank's
 // own buffer included), see kvb_peer_ring in the header.  A ring buffer holds [slot = call & 1][sender] blocks of
-// m[rows] | l[rows] | o[rows][D]; every fp32 value travels in one aligned 8-byte word together with the number
-// of the call that produced it (value in the low half, call number in the high half).  An 8-byte store arrives
-// whole, so a reader that sees the expected call number in a word also sees its value: no fences, no separate
-// flags, the latency of the exchange is one store across NVLink.
-constexpr int kRingMaxWorld = 16;
+// {m, l}[rows] | o[rows][D]; every fp32 value travels in one aligned 8-byte word together with the number of the
+// call that produced it (value in the low half, call number in the high half).  An 8-byte word arrives whole, so
+// a reader that sees the expected call number in a word also sees its value: no fences, no separate flags, the
+// latency of the exchange is one store across NVLink.  Words move in pairs (16-byte accesses, each half carrying
+// its own call number).
+constexpr int kRingMaxWorld = 16, kRingGroup = 8;
 struct PushTarget {
-    unsigned long long* const* peer_bufs;  // device array of `world` pointers, or null: no push
-    uint32_t* state;                       // local words: [0] calls completed, [2] CTAs of this call that are done
-    const unsigned long long* local_buf;   // this rank's own ring buffer (what the peers write)
-    uint32_t max_spins;                    // bound of the wait for a peer's word
+    unsigned long long* peers[kRingMaxWorld];  // ring buffer of every rank, in rank order (kernel parameter space)
+    uint32_t* state;                           // local words: [0] calls completed, [2] CTAs of this call that are done
+    const unsigned long long* local_buf;       // this rank's own ring buffer (what the peers write)
+    uint32_t max_spins;                        // bound of the wait for the peers' words
     uint32_t* error_word;
-    int rank, world;
+    int rank, world;                           // world 0: no push
 };
-__device__ __forceinline__ void ring_store(unsigned long long* p, float v, uint32_t call) {
-    *reinterpret_cast<volatile unsigned long long*>(p) = (static_cast<unsigned long long>(call) << 32) | __float_as_uint(v);
+__device__ __forceinline__ void ring_store2(unsigned long long* p, float a, float b, uint32_t call) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(__float_as_uint(a)), "r"(call), "r"(__float_as_uint(b)),
+                 "r"(call)
+                 : "memory");
 }
-
-__device__ __forceinline__ bool ring_load(const unsigned long long* p, uint32_t call, uint32_t max_spins, float& v) {
-    for (uint32_t i = 0; i < max_spins; ++i) {
-        const unsigned long long w = *reinterpret_cast<const volatile unsigned long long*>(p);
-        if (static_cast<uint32_t>(w >> 32) == call) { v = __uint_as_float(static_cast<uint32_t>(w)); return true; }
-        __nanosleep(32);
-    }
-    v = 0.0f;
-    return false;
+__device__ __forceinline__ uint4 ring_load2(const unsigned long long* p) {
+    uint4 w;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(p) : "memory");
+    return w;
 }
+__device__ __forceinline__ bool ring_arrived(const uint4& w, uint32_t call) { return w.y == call && w.w == call; }
 
 __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
                                                                   const float* __restrict__ ws_o, int parts, int T, int q_heads,
@@ -671,6 +670,8 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
     const int G = q_heads / kv_heads, tq = row / q_heads, qh = row % q_heads, head = qh / G, gq = qh % G;
     const int R = tq * G + gq, zb = R / kRows, r = R % kRows;
     const int64_t base = (static_cast<int64_t>(head) * zblocks + zb) * parts * kRows + r;
+    // the number of this call on the ring (read early: its latency hides behind the partial loads)
+    const uint32_t call = push.world > 0 && warp == 0 ? *reinterpret_cast<volatile uint32_t*>(push.state) + 1u : 0u;
     // every warp finds the global maximum (parts <= 64: two loads per lane)
     float m = lane < parts ? ws_m[base + static_cast<int64_t>(lane) * kRows] : -INFINITY;
     if (lane + 32 < parts) m = fmaxf(m, ws_m[base + static_cast<int64_t>(lane + 32) * kRows]);
@@ -709,42 +710,88 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
         acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
         l += sl[w];
     }
-    if (push.peer_bufs != nullptr) {
+    if (push.world > 0) {
         // Sharded decode: this CTA owns one query row on every rank.  It stores its partial of the row straight into
         // every peer's ring buffer, waits (bounded) for the peers' partials of the same row in its own ring buffer,
-        // merges them with its own, normalises, rotates back and stores -- send, receive and merge in one kernel.
-        const uint32_t call = *reinterpret_cast<volatile uint32_t*>(push.state) + 1u, slot = call & 1u;
+        // merges all of them in rank order (every rank computes the same bits), normalises, rotates back and
+        // stores -- send, receive and merge in one kernel.  All loads of a polling round are issued before any is
+        // examined, so a round costs one memory latency whatever the number of ranks.
+        const uint32_t slot = call & 1u;
         const int rows = T * q_heads;
         const int64_t block = static_cast<int64_t>(rows) * (D + 2);
+        const int64_t ml_off = 2 * static_cast<int64_t>(row), o_off = 2 * static_cast<int64_t>(rows) + static_cast<int64_t>(row) * D + 4 * lane;
         const float mine = m * kLn2;  // natural-log units, like every exported partial
-        for (int p = 0; p < push.world; ++p) {
-            if (p == push.rank) continue;
-            unsigned long long* dst = push.peer_bufs[p] + (static_cast<int64_t>(slot) * push.world + push.rank) * block;
-            if (lane == 0) { ring_store(dst + row, mine, call); ring_store(dst + rows + row, l, call); }
-            unsigned long long* o = dst + 2 * rows + static_cast<int64_t>(row) * D + 4 * lane;
-            ring_store(o, acc.x, call); ring_store(o + 1, acc.y, call); ring_store(o + 2, acc.z, call); ring_store(o + 3, acc.w, call);
-        }
-        bool ok = true;
-        float pm[kRingMaxWorld], gm = mine;
-        for (int p = 0; p < push.world; ++p) {
-            pm[p] = mine;
-            if (p == push.rank) continue;
-            ok &= ring_load(push.local_buf + (static_cast<int64_t>(slot) * push.world + p) * block + row, call, push.max_spins, pm[p]);
-            gm = fmaxf(gm, pm[p]);
-        }
-        const float w0 = gm == -INFINITY ? 0.0f : __expf(mine - gm);
-        float gl = w0 * l;
-        float4 go = make_float4(w0 * acc.x, w0 * acc.y, w0 * acc.z, w0 * acc.w);
-        for (int p = 0; p < push.world; ++p) {
-            if (p == push.rank) continue;
-            const unsigned long long* blk = push.local_buf + (static_cast<int64_t>(slot) * push.world + p) * block;
-            float pl, v[4];
-            ok &= ring_load(blk + rows + row, call, push.max_spins, pl);
+        const int64_t my_block = (static_cast<int64_t>(slot) * push.world + push.rank) * block;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) ok &= ring_load(blk + 2 * rows + static_cast<int64_t>(row) * D + 4 * lane + j, call, push.max_spins, v[j]);
-            const float w = gm == -INFINITY ? 0.0f : __expf(pm[p] - gm);
-            gl += w * pl;
-            go.x += w * v[0]; go.y += w * v[1]; go.z += w * v[2]; go.w += w * v[3];
+        for (int p = 0; p < kRingMaxWorld; ++p) {
+            if (p >= push.world || p == push.rank) continue;
+            unsigned long long* dst = push.peers[p] + my_block;
+            ring_store2(dst + o_off, acc.x, acc.y, call);
+            ring_store2(dst + o_off + 2, acc.z, acc.w, call);
+            if (lane == 0) ring_store2(dst + ml_off, mine, l, call);
+        }
+        const unsigned long long* in = push.local_buf + static_cast<int64_t>(slot) * push.world * block;
+        const uint32_t everyone = (push.world >= 32 ? 0xffffffffu : (1u << push.world) - 1u) & ~(1u << push.rank);
+        uint32_t spins = 0;
+        // (m, l) of every rank
+        float rm[kRingMaxWorld], rl[kRingMaxWorld];
+        uint32_t pending = everyone;
+        while (pending != 0u && spins < push.max_spins) {
+            uint4 w[kRingMaxWorld];
+#pragma unroll
+            for (int p = 0; p < kRingMaxWorld; ++p)
+                if (pending >> p & 1u) w[p] = ring_load2(in + p * block + ml_off);
+#pragma unroll
+            for (int p = 0; p < kRingMaxWorld; ++p)
+                if ((pending >> p & 1u) && ring_arrived(w[p], call)) {
+                    rm[p] = __uint_as_float(w[p].x);
+                    rl[p] = __uint_as_float(w[p].z);
+                    pending &= ~(1u << p);
+                }
+            if (pending != 0u) { ++spins; __nanosleep(32); }
+        }
+        bool ok = pending == 0u;
+        float gm = mine;
+#pragma unroll
+        for (int p = 0; p < kRingMaxWorld; ++p)
+            if (everyone >> p & 1u) gm = fmaxf(gm, ok ? rm[p] : mine);
+        float gl = 0.0f;
+        float4 go = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int g = 0; g < kRingMaxWorld; g += kRingGroup) {
+            if (g >= push.world || !ok) continue;
+            uint4 a[kRingGroup], b[kRingGroup];
+            pending = everyone >> g & ((1u << kRingGroup) - 1u);
+            while (pending != 0u && spins < push.max_spins) {
+#pragma unroll
+                for (int i = 0; i < kRingGroup; ++i)
+                    if (pending >> i & 1u) {
+                        a[i] = ring_load2(in + (g + i) * block + o_off);
+                        b[i] = ring_load2(in + (g + i) * block + o_off + 2);
+                    }
+                uint32_t still = 0u;
+#pragma unroll
+                for (int i = 0; i < kRingGroup; ++i)
+                    if ((pending >> i & 1u) && !(ring_arrived(a[i], call) && ring_arrived(b[i], call))) still |= 1u << i;
+                pending = still;
+                if (pending != 0u) { ++spins; __nanosleep(32); }
+            }
+            ok = pending == 0u;
+#pragma unroll
+            for (int i = 0; i < kRingGroup; ++i) {
+                const int p = g + i;
+                if (p >= push.world || !ok) continue;
+                if (p == push.rank) {
+                    const float w = gm == -INFINITY ? 0.0f : __expf(mine - gm);
+                    gl += w * l;
+                    go.x += w * acc.x; go.y += w * acc.y; go.z += w * acc.z; go.w += w * acc.w;
+                } else {
+                    const float w = gm == -INFINITY ? 0.0f : __expf(rm[p] - gm);
+                    gl += w * rl[p];
+                    go.x += w * __uint_as_float(a[i].x); go.y += w * __uint_as_float(a[i].z);
+                    go.z += w * __uint_as_float(b[i].x); go.w += w * __uint_as_float(b[i].z);
+                }
+            }
         }
         ok = __all_sync(0xffffffffu, ok);
         if (!ok && lane == 0 && push.error_word != nullptr) atomicOr(push.error_word, KVB_ERR_WAIT_TIMEOUT);
@@ -904,7 +951,7 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     const int total_rows = T * layer->q_heads;
     reduce_kernel<<<total_rows, kReduceWarps * 32, 0, stream>>>(P.ws_m, P.ws_l, P.ws_o, parts, T, layer->q_heads, layer->kv_heads, Z,
                                                             layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o,
-                                                            push != nullptr ? *push : PushTarget{nullptr, nullptr, nullptr, 0u, nullptr, 0, 0});
+                                                            push != nullptr ? *push : PushTarget{});
     KVB_CUDA_OK(cudaGetLastError());
     return KVB_OK;
 }
@@ -995,13 +1042,24 @@ extern "C" size_t kvb_peer_ring_bytes(int world, int q_heads, int head_dim) {
 extern "C" int kvb_attn_decode_sharded(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
                                        void* workspace, const kvb_peer_ring* ring, void* out, void* stream) {
     using namespace kvb;
-    if (ring == nullptr || ring->peer_bufs_dev == nullptr || ring->local_buf == nullptr || ring->state == nullptr || out == nullptr)
+    if (ring == nullptr || ring->peer_bufs == nullptr || ring->local_buf == nullptr || ring->state == nullptr || out == nullptr)
         return fail(KVB_EINVAL, "kvb_attn_decode_sharded: null ring / buffers / out");
     if (ring->world < 1 || ring->world > kRingMaxWorld || ring->rank < 0 || ring->rank >= ring->world)
         return fail(KVB_EINVAL, "kvb_attn_decode_sharded: rank %d of world %d (1..%d ranks)", ring->rank, ring->world, kRingMaxWorld);
-    const PushTarget push{reinterpret_cast<unsigned long long* const*>(ring->peer_bufs_dev), ring->state,
-                          static_cast<const unsigned long long*>(ring->local_buf), ring->max_spins ? ring->max_spins : (1u << 22),
-                          layer->error_word, ring->rank, ring->world};
+    PushTarget push{};
+    for (int p = 0; p < ring->world; ++p) {
+        if (ring->peer_bufs[p] == nullptr || (reinterpret_cast<uintptr_t>(ring->peer_bufs[p]) & 15u) != 0)
+            return fail(KVB_EINVAL, "kvb_attn_decode_sharded: ring buffer of rank %d is null or not 16-byte aligned", p);
+        push.peers[p] = static_cast<unsigned long long*>(ring->peer_bufs[p]);
+    }
+    if ((reinterpret_cast<uintptr_t>(ring->local_buf) & 15u) != 0)
+        return fail(KVB_EINVAL, "kvb_attn_decode_sharded: local ring buffer is not 16-byte aligned");
+    push.state = ring->state;
+    push.local_buf = static_cast<const unsigned long long*>(ring->local_buf);
+    push.max_spins = ring->max_spins ? ring->max_spins : (1u << 20);
+    push.error_word = layer != nullptr ? layer->error_word : nullptr;
+    push.rank = ring->rank;
+    push.world = ring->world;
     return launch_attention(layer, q, pos_dev, pos_dev, 1, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr, nullptr,
                             static_cast<cudaStream_t>(stream), "kvb_attn_decode_sharded", &push);
 }

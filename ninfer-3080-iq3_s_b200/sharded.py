@@ -102,9 +102,9 @@ class PeerRing:
         from . import capi
 
         self.local_buf, self.rank, self.world, self._keep = local_buf, rank, world, keep
-        self.peer_ptrs = torch.tensor(list(peer_ptrs), dtype=torch.int64, device=device)
+        self.peer_ptrs = (C.c_void_p * world)(*[int(p) for p in peer_ptrs])
         self.state = torch.zeros(4, dtype=torch.int32, device=device)
-        self.c = capi.kvb_peer_ring(peer_bufs_dev=self.peer_ptrs.data_ptr(), local_buf=local_buf.data_ptr(),
+        self.c = capi.kvb_peer_ring(peer_bufs=self.peer_ptrs, local_buf=local_buf.data_ptr(),
                                     state=self.state.data_ptr(), rank=rank, world=world, max_spins=max_spins)
         self._C = C
 

@@ -278,3 +278,54 @@ def test_sharded_decode_ring_loopback_and_bounded_wait():
     assert tw.gpu.errors() & capi.ERR_WAIT_TIMEOUT
     assert not out.any()
     assert int(ring2.state[0].item()) == 1
+
+
+def test_sharded_decode_ring_merges_arrived_peers_in_rank_order():
+    """Receive + merge of kvb_attn_decode_sharded with 4 ranks, checked on one GPU without any waiting: the three
+    peers' words (value | call number, the ring's wire format) are placed in this rank's ring buffer before the
+    launch, as if they had arrived early.  The result must equal kvb_merge_partials over the four partials in rank
+    order bit for bit, for both ring slots, and what this rank sends must show up in every peer's buffer."""
+    import torch
+
+    sh = pkg().sharded
+    cache = pkg().cache
+    QH, D, world, rank = 24, 128, 4, 2
+    scale = 1.0 / np.sqrt(D)
+    lens = [700, 1100, 900, 333]
+    twins = []
+    for r in range(world):
+        tw = Twin(D=D, H=4, QH=QH, capacity_tokens=lens[r], seed=300 + r)
+        tw.append(orc.synth_kv(310 + r, lens[r], 4, D, 1), orc.synth_kv(310 + r, lens[r], 4, D, 2))
+        twins.append(tw)
+    dev = twins[0].dev
+    ring = sh.PeerRing.loopback(QH, D, dev, world=world, rank=rank, max_spins=1000)
+    dec = sh.RingShardedDecode(twins[rank].gpu, ring)
+    block = QH * (D + 2)
+    for call in (1, 2, 3):
+        qd = torch.from_numpy(orc.synth_q(320 + call, 1, QH, D)[0]).to(dev)
+        ms, ls, os_ = [], [], []
+        for r in range(world):
+            pos = torch.tensor([lens[r] - 1], dtype=torch.int32, device=dev)
+            m, l, o = twins[r].gpu.attn_decode_partial(qd, pos, scale, lens[r])
+            ms.append(m.clone()); ls.append(l.clone()); os_.append(o.clone())
+        want = cache.merge_partials(torch.stack(ms), torch.stack(ls), torch.stack(os_))
+        words = ring.local_buf.view(torch.int32).view(2, world, block, 2)
+        for r in range(world):
+            if r == rank:
+                continue
+            vals = torch.cat([torch.stack([ms[r], ls[r]], dim=1).reshape(-1), os_[r].reshape(-1)])
+            words[call & 1, r, :, 0] = vals.view(torch.int32)
+            words[call & 1, r, :, 1] = call
+        out = torch.empty_like(qd)
+        pos = torch.tensor([lens[rank] - 1], dtype=torch.int32, device=dev)
+        dec.attn_decode(qd, pos, scale, lens[rank], out)
+        torch.cuda.synchronize()
+        assert twins[rank].gpu.errors() == 0
+        assert torch.equal(out, want), call
+        mine = torch.cat([torch.stack([ms[rank], ls[rank]], dim=1).reshape(-1), os_[rank].reshape(-1)]).view(torch.int32)
+        for r in range(world):
+            if r == rank:
+                continue
+            sent = ring._keep[r].view(torch.int32).view(2, world, block, 2)[call & 1, rank]
+            assert torch.equal(sent[:, 0], mine) and bool((sent[:, 1] == call).all()), (call, r)
+    assert int(ring.state[0].item()) == 3
