@@ -253,13 +253,14 @@ __device__ __forceinline__ void softmax_block(float (&s)[NB][NG][4], Acc<NB>& ac
     }
 }
 
-// One sealed page (64 keys) of one KV head, staged in shared memory at `pg`.
+// One sealed page (64 keys) of one KV head, staged in shared memory at `pg`: qk_page fills s with the masked
+// logits (log2 units), softmax_block turns them into p, pv_page accumulates p V.  (Computing the logits of the
+// next page between the softmax and the P V of this one was measured slower: more registers, no more overlap.)
 template <int NB, bool kOther>
-__device__ __forceinline__ void process_page(const uint8_t* pg, const uint8_t* scratch, const QInt<NB>& qf, Acc<NB>& acc,
-                                             int lane, bool need_mask, int first_pos, const int (&row_lim)[NB][2],
-                                             int key_begin, int key_end) {
+__device__ __forceinline__ void qk_page(const uint8_t* pg, const uint8_t* scratch, const QInt<NB>& qf, float (&s)[NB][4][4],
+                                        int lane, bool need_mask, int first_pos, const int (&row_lim)[NB][2], int key_begin,
+                                        int key_end) {
     const int g = lane >> 2, t = lane & 3;
-    float s[NB][4][4];
     // ---- QK on the int8 tensor path: A = packed code bytes of keys (g, g+8) masked to their low / high nibbles,
     //      B = 8-bit digits of (q' scale_K)^T; exact 32-bit accumulation
 #pragma unroll
@@ -314,7 +315,11 @@ __device__ __forceinline__ void process_page(const uint8_t* pg, const uint8_t* s
             }
         }
     }
-    softmax_block<NB, 4>(s, acc);
+}
+
+template <int NB>
+__device__ __forceinline__ void pv_page(const uint8_t* pg, const float (&s)[NB][4][4], Acc<NB>& acc, int lane) {
+    const int g = lane >> 2, t = lane & 3;
     // ---- PV: A = V codes^T (dims x keys), B = (p scale_V)^T.  V scale page rows: [other other scale zp] per key
 #pragma unroll
     for (int grp = 0; grp < 4; ++grp) {
@@ -440,24 +445,81 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y, zb = blockIdx.z, split = blockIdx.x;
     const int G = L.q_heads / L.kv_heads;
+    grid_dependency_wait();  // q, the positions and the cache come from the kernels before this one
+    // ---- order of the first memory requests: the few bytes everything waits for (positions, q rows, page table
+    //      entries) go out first, then the first page of every warp, then -- after the rotation of q, about a
+    //      microsecond later -- the second page.  At short contexts the whole cache is requested in this first burst:
+    //      requested in this order the small loads do not queue behind it and all first pages land before any second.
+    uint16_t qraw[NB][4];
+    int qpos[NB];
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {  // warp w prepares rows w and w + 8 of the block
+        const int R = zb * kRows + warp + kWarps * i, tq = R / G, gq = R % G;
+        qpos[i] = -1;
+        qraw[i][0] = qraw[i][1] = qraw[i][2] = qraw[i][3] = 0;
+        if (tq < P.T) {
+            const uint16_t* qrow = P.q + (static_cast<int64_t>(tq) * L.q_heads + head * G + gq) * D;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) qraw[i][j] = qrow[lane + 32 * j];
+            qpos[i] = P.pos[tq];
+        }
+    }
     const int kv_total = *P.total_pos + 1;
     const int key_end = min(P.key_end, kv_total), key_begin = max(P.key_begin, 0);
     const int sealed_pages = 2 * (kv_total / kTile);
 
+    uint64_t* bars = sm.bars[warp];
+    if (lane == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        mbar_fence_init();
+    }
+    const int32_t* tbl = L.table();
+    auto issue = [&](int32_t page, int slot) {  // lane 0: four bulk copies of one page into a slot
+        uint8_t* dst = sm.slots[warp][slot];
+        mbar_expect_tx(&bars[slot], kPageBytes);
+        bulk_g2s(dst + kKCodeOff, L.k_code + page_head_offset(64, L.kv_heads, page, head), 4096, &bars[slot]);
+        bulk_g2s(dst + kVCodeOff, L.v_code + page_head_offset(64, L.kv_heads, page, head), 4096, &bars[slot]);
+        bulk_g2s(dst + kKScaleOff, L.k_scale + page_head_offset(5, L.kv_heads, page, head), 640, &bars[slot]);
+        bulk_g2s(dst + kVScaleOff, L.v_scale + page_head_offset(4, L.kv_heads, page, head), 512, &bars[slot]);
+    };
+    // Page table entries are read 32 at a time, one per lane, a full batch ahead of their use: lane l of `ids`
+    // knows the physical page of logical page ids_base + l, `ids_next` the 32 after those.
+    int w0 = 0, w1 = 0, ids_base = 0;
+    int32_t ids = -1, ids_next = -1;
+    auto load_ids = [&](int base) -> int32_t { return base + lane < w1 ? L.page_of(tbl, base + lane) : -1; };
+    auto page_id = [&](int lp) -> int32_t {  // whole warp; lp in [ids_base, ids_base + 64)
+        const int k = lp - ids_base;
+        const int32_t a = __shfl_sync(0xffffffffu, ids, k & 31), b = __shfl_sync(0xffffffffu, ids_next, k & 31);
+        return k < 32 ? a : b;
+    };
+    uint32_t ok_mask = 0;  // bit s: slot s holds a page in flight / ready
+    int32_t second_page = -1;
+    if (split < P.nsplit) {  // sealed pages of this CTA, then of this warp
+        const int pb = min(key_begin / kPage, sealed_pages), pe = min((key_end + kPage - 1) / kPage, sealed_pages);
+        const int n = max(pe - pb, 0);
+        const int c0 = pb + static_cast<int>(static_cast<int64_t>(n) * split / P.nsplit);
+        const int c1 = pb + static_cast<int>(static_cast<int64_t>(n) * (split + 1) / P.nsplit);
+        w0 = c0 + (c1 - c0) * warp / kWarps;
+        w1 = c0 + (c1 - c0) * (warp + 1) / kWarps;
+        ids_base = w0;
+        ids = load_ids(w0);
+        ids_next = load_ids(w0 + 32);
+        const int32_t p0 = __shfl_sync(0xffffffffu, ids, 0), p1 = __shfl_sync(0xffffffffu, ids, 1);  // -1 beyond w1 or bad
+        ok_mask = (p0 >= 0 ? 1u : 0u) | (p1 >= 0 ? 2u : 0u);
+        second_page = p1;
+        if (lane == 0 && p0 >= 0) issue(p0, 0);
+    }
+
     // ---- q' = H q * scale * log2(e) for the rows of this block, stored in fragment order
-    for (int r = warp; r < 8 * NB; r += kWarps) {
-        const int R = zb * kRows + r, tq = R / G, gq = R % G;
-        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        int rp = -1;
-        if (tq < P.T) {
-            const uint16_t* qrow = P.q + (static_cast<int64_t>(tq) * L.q_heads + head * G + gq) * D;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                v[j] = L.dtype == KVB_DTYPE_BF16 ? in_to_f32<true>(qrow[lane + 32 * j]) : in_to_f32<false>(qrow[lane + 32 * j]);
-            hadamard_warp<D>(v, lane);
-            rp = P.pos[tq];
-        }
-        if (lane == 0) sm.row_pos[r] = rp;
+    for (int i = 0; i < NB; ++i) {
+        const int r = warp + kWarps * i;
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = L.dtype == KVB_DTYPE_BF16 ? in_to_f32<true>(qraw[i][j]) : in_to_f32<false>(qraw[i][j]);
+        hadamard_warp<D>(v, lane);  // rows beyond T are zeros and stay zeros
+        if (lane == 0) sm.row_pos[r] = qpos[i];
         float* dst = reinterpret_cast<float*>(sm.qfrag);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -465,12 +527,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
             dst[(((r >> 3) * 8 + ((d & 31) >> 2)) * 32 + (r & 7) * 4 + (d >> 5)) * 4 + (d & 3)] = v[j] * P.scale_log2;
         }
     }
-    uint64_t* bars = sm.bars[warp];
-    if (lane == 0) {
-        mbar_init(&bars[0], 1);
-        mbar_init(&bars[1], 1);
-        mbar_fence_init();
-    }
+    if (lane == 0 && second_page >= 0) issue(second_page, 1);
+    launch_dependents();  // the reduce kernel may take its place on the SMs; it waits for this grid's completion
     __syncthreads();
 
     const int g = lane >> 2, t = lane & 3;
@@ -497,35 +555,16 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
     bool timed_out = false;
 
     if (split < P.nsplit) {
-        // ---- sealed pages of this CTA, then of this warp
-        const int pb = min(key_begin / kPage, sealed_pages), pe = min((key_end + kPage - 1) / kPage, sealed_pages);
-        const int n = max(pe - pb, 0);
-        const int c0 = pb + static_cast<int>(static_cast<int64_t>(n) * split / P.nsplit);
-        const int c1 = pb + static_cast<int>(static_cast<int64_t>(n) * (split + 1) / P.nsplit);
-        const int w0 = c0 + (c1 - c0) * warp / kWarps, w1 = c0 + (c1 - c0) * (warp + 1) / kWarps;
-        const int32_t* tbl = L.table();
         uint8_t* scratch = sm.scratch[warp];
-        auto issue = [&](int lp, int slot) -> bool {  // lane 0: four bulk copies of one page into a slot
-            const int32_t page = L.page_of(tbl, lp);
-            if (page < 0) return false;
-            uint8_t* dst = sm.slots[warp][slot];
-            mbar_expect_tx(&bars[slot], kPageBytes);
-            bulk_g2s(dst + kKCodeOff, L.k_code + page_head_offset(64, L.kv_heads, page, head), 4096, &bars[slot]);
-            bulk_g2s(dst + kVCodeOff, L.v_code + page_head_offset(64, L.kv_heads, page, head), 4096, &bars[slot]);
-            bulk_g2s(dst + kKScaleOff, L.k_scale + page_head_offset(5, L.kv_heads, page, head), 640, &bars[slot]);
-            bulk_g2s(dst + kVScaleOff, L.v_scale + page_head_offset(4, L.kv_heads, page, head), 512, &bars[slot]);
-            return true;
-        };
-        uint32_t ok_mask = 0;  // bit s: slot s holds a page in flight / ready (lane 0 decides, broadcast below)
-        if (lane == 0) {
-            if (w0 < w1 && issue(w0, 0)) ok_mask |= 1u;
-            if (w0 + 1 < w1 && issue(w0 + 1, 1)) ok_mask |= 2u;
-        }
-        ok_mask = __shfl_sync(0xffffffffu, ok_mask, 0);
         uint32_t phase[2] = {0, 0};
         int cur_tile = -1;
         for (int lp = w0; lp < w1; ++lp) {
             const int slot = (lp - w0) & 1;
+            if (lp - ids_base >= 32) {
+                ids = ids_next;
+                ids_base += 32;
+                ids_next = load_ids(ids_base + 32);
+            }
             const bool valid = (ok_mask >> slot) & 1u;
             if (valid) {
                 if (!mbar_wait_bounded(&bars[slot], phase[slot])) { timed_out = true; break; }
@@ -544,16 +583,19 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
                 }
                 const int first = lp * kPage;
                 const bool need_mask = first + kPage - 1 > min_lim || first < key_begin || first + kPage > key_end;
-                process_page<NB, kOther>(pg, scratch, qi, acc, lane, need_mask, first, row_lim, key_begin, key_end);
+                float s[NB][4][4];
+                qk_page<NB, kOther>(pg, scratch, qi, s, lane, need_mask, first, row_lim, key_begin, key_end);
+                softmax_block<NB, 4>(s, acc);
+                pv_page<NB>(pg, s, acc, lane);
             }
             // refill this slot with the page after next; the generic-proxy reads above must be ordered first
             __syncwarp();
-            uint32_t nv = 0;
-            if (lane == 0 && lp + 2 < w1) {
+            const int32_t np = lp + 2 < w1 ? page_id(lp + 2) : -1;
+            const uint32_t nv = np >= 0 ? 1u : 0u;
+            if (lane == 0 && nv) {
                 fence_proxy_async();
-                nv = issue(lp + 2, slot) ? 1u : 0u;
+                issue(np, slot);
             }
-            nv = __shfl_sync(0xffffffffu, nv, 0);
             ok_mask = (ok_mask & ~(1u << slot)) | (nv << slot);
         }
         if (timed_out) {
@@ -595,32 +637,34 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
         }
         float* ob = mbuf + 3 * kRows + (8 * nb + 2 * t) * kORow + 16 * g;
 #pragma unroll
-        for (int mb = 0; mb < 8; ++mb) {
-            ob[mb] = acc.o[nb][mb][0];
-            ob[kORow + mb] = acc.o[nb][mb][1];
-            ob[8 + mb] = acc.o[nb][mb][2];
-            ob[kORow + 8 + mb] = acc.o[nb][mb][3];
+        for (int e = 0; e < 4; ++e) {  // component e: row 2t + (e & 1), dims 16g + 8 (e >> 1) ..
+            float* dst = ob + (e & 1) * kORow + (e >> 1) * 8;
+            *reinterpret_cast<float4*>(dst) = make_float4(acc.o[nb][0][e], acc.o[nb][1][e], acc.o[nb][2][e], acc.o[nb][3][e]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(acc.o[nb][4][e], acc.o[nb][5][e], acc.o[nb][6][e], acc.o[nb][7][e]);
         }
     }
     __syncthreads();
     const float* all = reinterpret_cast<const float*>(sm.slots);
     const int64_t pidx = ((static_cast<int64_t>(head) * gridDim.z + zb) * (P.nsplit + 1) + split) * kRows;
-    for (int e = threadIdx.x; e < 8 * NB * D; e += kThreads) {
-        const int row = e / D, d = e % D;
+    for (int e = threadIdx.x; e < 8 * NB * (D / 4); e += kThreads) {  // one thread: four dims of one row
+        const int row = e / (D / 4), d = 4 * (e % (D / 4));
         float m = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) m = fmaxf(m, all[w * kWarpFloats + row]);
-        float o = 0.0f, l = 0.0f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        float l = 0.0f;
         if (m != -INFINITY) {
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) {
                 const float* wb = all + w * kWarpFloats;
                 const float wt = fast_exp2(wb[row] - m);  // exp2(-inf) = 0 for a warp that saw no key
+                const float4 v = *reinterpret_cast<const float4*>(wb + 3 * kRows + row * kORow + d);
+                const float z = wb[2 * kRows + row];
                 l += wt * wb[kRows + row];
-                o += wt * (wb[3 * kRows + row * kORow + d] + wb[2 * kRows + row]);
+                o.x += wt * (v.x + z); o.y += wt * (v.y + z); o.z += wt * (v.z + z); o.w += wt * (v.w + z);
             }
         }
-        P.ws_o[(pidx + row) * D + d] = o;
+        *reinterpret_cast<float4*>(P.ws_o + (pidx + row) * D + d) = o;
         if (d == 0) { P.ws_m[pidx + row] = m; P.ws_l[pidx + row] = l; }
     }
 }
@@ -670,13 +714,13 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
     const int G = q_heads / kv_heads, tq = row / q_heads, qh = row % q_heads, head = qh / G, gq = qh % G;
     const int R = tq * G + gq, zb = R / kRows, r = R % kRows;
     const int64_t base = (static_cast<int64_t>(head) * zblocks + zb) * parts * kRows + r;
+    grid_dependency_wait();  // launched while the attention kernel still runs: its partials are complete from here on
+    launch_dependents();
     // the number of this call on the ring (read early: its latency hides behind the partial loads)
     const uint32_t call = push.world > 0 && warp == 0 ? *reinterpret_cast<volatile uint32_t*>(push.state) + 1u : 0u;
     // every warp finds the global maximum (parts <= 64: two loads per lane)
     float m = lane < parts ? ws_m[base + static_cast<int64_t>(lane) * kRows] : -INFINITY;
     if (lane + 32 < parts) m = fmaxf(m, ws_m[base + static_cast<int64_t>(lane + 32) * kRows]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     float4 v[kMaxPartsPerWarp];
     float pm[kMaxPartsPerWarp], pl[kMaxPartsPerWarp];
 #pragma unroll
@@ -688,6 +732,8 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
         pl[i] = on ? ws_l[idx] : 0.0f;
         v[i] = on ? *reinterpret_cast<const float4*>(ws_o + idx * D + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));  // after the loads are in flight
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float l = 0.0f;
     if (m != -INFINITY) {
@@ -945,14 +991,11 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
         opted = true;
     }
     const dim3 grid(parts, layer->kv_heads, Z);
-    if (upper) attn_kernel<2, false><<<grid, kThreads, smem, stream>>>(P);
-    else attn_kernel<1, false><<<grid, kThreads, smem, stream>>>(P);
-    KVB_CUDA_OK(cudaGetLastError());
+    KVB_CUDA_OK(launch_early(upper ? attn_kernel<2, false> : attn_kernel<1, false>, grid, dim3(kThreads), smem, stream, P));
     const int total_rows = T * layer->q_heads;
-    reduce_kernel<<<total_rows, kReduceWarps * 32, 0, stream>>>(P.ws_m, P.ws_l, P.ws_o, parts, T, layer->q_heads, layer->kv_heads, Z,
-                                                            layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o,
-                                                            push != nullptr ? *push : PushTarget{});
-    KVB_CUDA_OK(cudaGetLastError());
+    KVB_CUDA_OK(launch_early(reduce_kernel, dim3(total_rows), dim3(kReduceWarps * 32), 0, stream, P.ws_m, P.ws_l, P.ws_o, parts, T,
+                             layer->q_heads, layer->kv_heads, Z, layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o,
+                             push != nullptr ? *push : PushTarget{}));
     return KVB_OK;
 }
 

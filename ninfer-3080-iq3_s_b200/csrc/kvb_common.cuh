@@ -75,6 +75,23 @@ struct LayerView {
     }
 };
 
+// Launch with programmatic stream serialization: the kernel may become resident while its predecessor in the
+// stream still runs and must call grid_dependency_wait() (kvb_ptx.cuh) before its first global memory access.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_early(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 LayerView make_view(const kvb_layer& L);
 int check_layer(const kvb_layer* L, const char* who);
 

@@ -66,6 +66,14 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may
+// start while its predecessor in the stream still runs (as soon as every CTA of the predecessor has called
+// launch_dependents or exited); it must call grid_dependency_wait() before touching anything the predecessor
+// writes: that returns when the predecessor has completed and its memory is visible.  Both are no-ops in a
+// kernel launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
