@@ -25,7 +25,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 D, H, QH, LAYERS, CTX = 128, 4, 24, 16, 32768
-TRAFFIC_BYTES_PER_TOKEN = 596.7
+TRAFFIC_BYTES_PER_TOKEN = 597.4
 SEALED_B, TAIL_B = 140, 512  # algorithmic bytes per sealed / open-tile token per KV head (codes + 12 B of axes | fp16 K+V rows)
 
 
@@ -564,15 +564,42 @@ def run_batch(args):
     for L, n in seqs:
         L.workspace(n + 8, 1)
 
-    def step():
+    def step_serial():
         for i, (L, n) in enumerate(seqs):
             L.attn_decode(q[i], poss[i], E.scale, n + 8, out=outs[i])
 
-    run, graphed = E.graph(step)
+    # The sequences are independent: dealt over a few streams (longest first) the fixed part of one call -- first
+    # requests, merge, the reduce kernel -- runs under the page streaming of the others.  Inside the captured graph
+    # the streams become parallel branches.
+    n_streams = max(1, min(args.streams or 4, len(seqs)))
+    side = [torch.cuda.Stream(device=E.dev) for _ in range(n_streams)]
+    lanes = E.pkg.sharded.deal_sequences([n for _, n in seqs], n_streams)
+
+    def step_streams():
+        cur = torch.cuda.current_stream()
+        fork = torch.cuda.Event()
+        fork.record(cur)
+        for st, lane in zip(side, lanes):
+            st.wait_event(fork)
+            with torch.cuda.stream(st):
+                for i in lane:
+                    L, n = seqs[i]
+                    L.attn_decode(q[i], poss[i], E.scale, n + 8, out=outs[i])
+            join = torch.cuda.Event()
+            join.record(st)
+            cur.wait_event(join)
+
+    run1, graphed1 = E.graph(step_serial)
+    for _ in range(3):
+        run1()
+    ms_serial = E.timed(run1, max(3, args.steps // 2))
+    ref = outs.clone()
+    run, graphed = E.graph(step_streams)
     with ClockSampler(E.local) as clk:
         for _ in range(max(args.warmup, 3)):
             run()
         ms = E.timed(run, args.steps)
+    same = bool(torch.equal(ref, outs))
     peak, kind = peaks()
     total = sum(decode_bytes(n) for n in lengths)
     E.finish({
@@ -583,7 +610,55 @@ def run_batch(args):
                    "total_tokens": sum(lengths), "q_heads": QH, "kv_heads": H, "head_dim": D, "parallelism": f"dp{E.world} (LPT by length, no collective)",
                    "l2": f"{total / 1e9:.2f} GB of KV per step"},
         "pct_of_hbm_peak": 100.0 * total / (ms * 1e-3) / 1e9 / (peak * E.world), "peak_kind": kind, "graph_captured": graphed,
+        "streams": n_streams, "ms_per_step_one_stream": ms_serial, "same_output_as_one_stream": same,
         "clocks": clk.summary(), "gpu_launches": args.steps * len(seqs) * 2,
+    })
+
+
+def run_append(args):
+    """Quantise-append alone: chunks of --chunk tokens (default 1,024, the prefill chunk; 4,096 = BASELINE config 0)
+    written at the same positions every step (a roll-back followed by a re-append), over enough layers that the
+    rows read and the planes written exceed L2."""
+    E = _Env()
+    torch = E.torch
+    T = args.chunk or 1024
+    layers_n = args.layers or max(4, min(64, int(300e6 // (T * H * D * 2 * 2)) + 1))
+    from oracle import kvarn_oracle as orc
+
+    lp = (T + 63) // 64 + 2
+    lp += lp & 1
+    layers = [E.pkg.KvarnLayer(D, H, QH, lp, torch.from_numpy(orc.shuffled_table(i, lp, lp)), sinkhorn_iters=args.iters, device=str(E.dev))
+              for i in range(layers_n)]
+    k = [E.synth(T, H) for _ in range(layers_n)]
+    v = [E.synth(T, H) for _ in range(layers_n)]
+    pos = torch.arange(0, T, dtype=torch.int32, device=E.dev)
+
+    def step():
+        for i, L in enumerate(layers):
+            L.append(k[i], v[i], pos)
+
+    run, graphed = E.graph(step)
+    with ClockSampler(E.local) as clk:
+        for _ in range(max(args.warmup, 3)):
+            run()
+        ms = E.timed(run, args.steps)
+    errs = sum(L.errors() for L in layers)
+    peak, kind = peaks()
+    tiles, tail = T // 128, T % 128
+    # rows read + planes written for the sealed tiles + stage rows written for the open tail (and, as the reference
+    # keeps them for roll-back, for the last sealed tile)
+    nbytes = 2 * T * H * D * 2 + tiles * 128 * H * 146 + (tail + (128 if tiles else 0)) * H * D * 2 * 2
+    us = ms * 1e3 / layers_n
+    E.finish({
+        "metric": "append_hbm_gbs", "value": nbytes / (us * 1e-6) / 1e9, "unit": "GB/s", "n_gpus": E.world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "us_per_layer": us, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"append_chunk{T}_iters{args.iters}", "layers": layers_n, "kv_heads": H, "head_dim": D,
+                   "l2": f"{layers_n} layers x {nbytes / 1e6:.1f} MB between revisits"},
+        "roofline": {"bound": "hbm", "achieved": nbytes / (us * 1e-6) / 1e9, "peak": peak, "peak_kind": kind, "unit": "GB/s",
+                     "frac": nbytes / (us * 1e-6) / 1e9 / peak, "traffic": None, "algorithmic_bytes_per_launch": nbytes},
+        "tokens_per_s": T / (us * 1e-6), "graph_captured": graphed, "error_words": errs, "clocks": clk.summary(),
+        "gpu_launches": args.steps * layers_n * (2 if T > 128 else 1),
     })
 
 
@@ -680,9 +755,13 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="decode32k", choices=["decode32k", "decodectx", "long379k", "batch32", "verify131k", "prefill262k"],
+    ap.add_argument("--workload", default="decode32k",
+                    choices=["decode32k", "decodectx", "long379k", "batch32", "verify131k", "prefill262k", "append"],
                     help="decode32k is the contract line; the others are BASELINE configs 4A, 4B, 2 and 3")
     ap.add_argument("--layers", type=int, default=0, help="layers held for long379k / verify131k (default 4)")
+    ap.add_argument("--streams", type=int, default=0, help="batch32: streams the independent sequences are dealt over (default 4)")
+    ap.add_argument("--chunk", type=int, default=0, help="append: tokens per append call (default 1024)")
+    ap.add_argument("--iters", type=int, default=0, help="append: Sinkhorn iterations of the encoder (0 = bit-exact regime, 16 = engine default)")
     ap.add_argument("--ctx", type=int, default=0, help="context for decodectx (default 131072) / prefix length for prefill262k (default 262144)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -690,7 +769,8 @@ def main():
     elif args.workload == "decode32k":
         run_gpu(args)
     else:
-        {"decodectx": run_decode_ctx, "long379k": run_long, "batch32": run_batch, "verify131k": run_verify, "prefill262k": run_prefill}[args.workload](args)
+        {"decodectx": run_decode_ctx, "long379k": run_long, "batch32": run_batch, "verify131k": run_verify, "prefill262k": run_prefill,
+         "append": run_append}[args.workload](args)
 
 
 if __name__ == "__main__":
