@@ -47,6 +47,7 @@ template <int D> struct AppendSmem {
     float red_hi[4 * D];
     float best_col[kSlice], best_row[kSlice];  // Sinkhorn factors of the slice being quantised
     float std_col[kSlice], std_row[kSlice], log_col[kSlice], log_row[kSlice], cur_col[kSlice], cur_row[kSlice];
+    float rcp_col[kSlice], rcp_row[kSlice];  // 1 / cur_col, 1 / cur_row
     float scal[8];
     __half ax_scale[S * kSlice];            // scale_axis / zp_axis / other_axis of every slice
     __half ax_zp[S * kSlice];
@@ -62,44 +63,97 @@ __device__ __forceinline__ float mat(const AppendSmem<D>& sm, int slice, int r, 
     return __half2float(sm.rows[tok * AppendSmem<D>::kStride + slice * kSlice + dim]);
 }
 
-// Sinkhorn variance balancing, `iters` rounds, GPU order of the reference
-// (kvarn128_codec.cuh:104-186 == bee_oracle.cpp:210-255).  Threads 0..127 own one column and one row.
+// Sinkhorn variance balancing, `iters` rounds, in the reference's order of updates
+// (kvarn128_codec.cuh:104-186 == bee_oracle.cpp:210-255): columns, rows, then "keep the best so far".
+// iters > 0 is the tolerance-checked regime (the reference's own CUDA kernel does not reproduce its host oracle
+// byte for byte there either), so the standard deviations are computed the fast way: every thread of the CTA
+// takes part, x / (s_col * s_row) becomes x * (1/s_col) * (1/s_row) with the reciprocals taken once per update
+// and the factor of the reduced-over axis pulled out of the sums, and partial sums meet in shared memory.
+// In memory terms a standard deviation runs either over the dims of a token (contiguous) or over the tokens of a
+// dim (strided); which of the two is the "row" depends on K / V (see mat()).
 template <int D, bool kValue>
 __device__ void sinkhorn(AppendSmem<D>& sm, int slice, int iters) {
+    constexpr int kStride = AppendSmem<D>::kStride;
     const int i = threadIdx.x;
-    auto col_std = [&](int c) {
-        float sum = 0.0f, sq = 0.0f;
-        const float sc = sm.cur_col[c];
-        for (int r = 0; r < kSlice; ++r) {
-            const float v = __fdiv_rn(mat<D, kValue>(sm, slice, r, c), __fmul_rn(sc, sm.cur_row[r]));
-            sum = __fadd_rn(sum, v);
-            sq = __fadd_rn(sq, __fmul_rn(v, v));
-        }
-        const float mean = __fdiv_rn(sum, 128.0f);
-        return sqrtf(fmaxf(__fdiv_rn(__fsub_rn(sq, __fmul_rn(__fmul_rn(128.0f, mean), mean)), 127.0f), 0.0f));
+    auto finish = [](float sum, float sq) {  // sample standard deviation of 128 values from their sum and sum of squares
+        const float mean = sum * (1.0f / 128.0f);
+        return sqrtf(fmaxf((sq - 128.0f * mean * mean) * (1.0f / 127.0f), 0.0f));
     };
-    auto row_std = [&](int r) {
-        float sum = 0.0f, sq = 0.0f;
-        const float sr = sm.cur_row[r];
-        for (int c = 0; c < kSlice; ++c) {
-            const float v = __fdiv_rn(mat<D, kValue>(sm, slice, r, c), __fmul_rn(sm.cur_col[c], sr));
-            sum = __fadd_rn(sum, v);
-            sq = __fadd_rn(sq, __fmul_rn(v, v));
+    // out[tok] = std over the 128 dims of x[tok][dim] * rd[dim] * rt[tok]; thread = (token, half of the dims)
+    auto std_over_dims = [&](float* out, const float* rt, const float* rd) {
+        const int t = i & 127, hf = i >> 7;
+        const __half* row = &sm.rows[t * kStride + slice * kSlice + hf * 64];
+        float s0 = 0.0f, s1 = 0.0f, q0 = 0.0f, q1 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 64; j += 8) {
+            const uint4 pk = *reinterpret_cast<const uint4*>(row + j);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float a = __low2float(h2[e]) * rd[hf * 64 + j + 2 * e], b = __high2float(h2[e]) * rd[hf * 64 + j + 2 * e + 1];
+                s0 += a; q0 = fmaf(a, a, q0);
+                s1 += b; q1 = fmaf(b, b, q1);
+            }
         }
-        const float mean = __fdiv_rn(sum, 128.0f);
-        return sqrtf(fmaxf(__fdiv_rn(__fsub_rn(sq, __fmul_rn(__fmul_rn(128.0f, mean), mean)), 127.0f), 0.0f));
+        sm.red_lo[hf * kTile + t] = s0 + s1;
+        sm.red_hi[hf * kTile + t] = q0 + q1;
+        __syncthreads();
+        if (i < kSlice) {
+            const float f = rt[i];
+            out[i] = finish((sm.red_lo[i] + sm.red_lo[kTile + i]) * f, (sm.red_hi[i] + sm.red_hi[kTile + i]) * f * f);
+        }
+        __syncthreads();
+    };
+    // out[dim] = std over the 128 tokens; thread = (dim pair, quarter of the tokens)
+    auto std_over_tokens = [&](float* out, const float* rt, const float* rd) {
+        const int b = i & 63, qtr = i >> 6;
+        float s0 = 0.0f, s1 = 0.0f, q0 = 0.0f, q1 = 0.0f;
+#pragma unroll 8
+        for (int c = qtr * 32; c < qtr * 32 + 32; ++c) {
+            const __half2 h = *reinterpret_cast<const __half2*>(&sm.rows[c * kStride + slice * kSlice + 2 * b]);
+            const float f = rt[c];
+            const float x0 = __low2float(h) * f, x1 = __high2float(h) * f;
+            s0 += x0; q0 = fmaf(x0, x0, q0);
+            s1 += x1; q1 = fmaf(x1, x1, q1);
+        }
+        sm.red_lo[qtr * kSlice + 2 * b] = s0; sm.red_lo[qtr * kSlice + 2 * b + 1] = s1;
+        sm.red_hi[qtr * kSlice + 2 * b] = q0; sm.red_hi[qtr * kSlice + 2 * b + 1] = q1;
+        __syncthreads();
+        if (i < kSlice) {
+            const float f = rd[i];
+            const float sum = (sm.red_lo[i] + sm.red_lo[kSlice + i]) + (sm.red_lo[2 * kSlice + i] + sm.red_lo[3 * kSlice + i]);
+            const float sq = (sm.red_hi[i] + sm.red_hi[kSlice + i]) + (sm.red_hi[2 * kSlice + i] + sm.red_hi[3 * kSlice + i]);
+            out[i] = finish(sum * f, sq * f * f);
+        }
+        __syncthreads();
+    };
+    // K: row = dim, col = token.  V: row = token, col = dim.
+    auto col_std = [&]() {
+        if constexpr (kValue) std_over_tokens(sm.std_col, sm.rcp_row, sm.rcp_col);
+        else std_over_dims(sm.std_col, sm.rcp_col, sm.rcp_row);
+    };
+    auto row_std = [&]() {
+        if constexpr (kValue) std_over_dims(sm.std_row, sm.rcp_row, sm.rcp_col);
+        else std_over_tokens(sm.std_row, sm.rcp_col, sm.rcp_row);
     };
     auto keep_best = [&]() {  // imbalance of the current factors; "<=" lets a later tie win
-        __syncthreads();
-        if (i == 0) {
+        if (i < 32) {
             float cmin = 3.402823466e+38f, cmax = 0.0f, rmin = 3.402823466e+38f, rmax = 0.0f;
-            for (int j = 0; j < kSlice; ++j) {
+#pragma unroll
+            for (int j = i; j < kSlice; j += 32) {
                 cmin = fminf(cmin, sm.std_col[j]); cmax = fmaxf(cmax, sm.std_col[j]);
                 rmin = fminf(rmin, sm.std_row[j]); rmax = fmaxf(rmax, sm.std_row[j]);
             }
-            const float imb = __fadd_rn(__fdiv_rn(cmax, fmaxf(cmin, 1e-8f)), __fdiv_rn(rmax, fmaxf(rmin, 1e-8f)));
-            sm.scal[1] = imb <= sm.scal[0] ? 1.0f : 0.0f;
-            if (imb <= sm.scal[0]) sm.scal[0] = imb;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                cmin = fminf(cmin, __shfl_xor_sync(0xffffffffu, cmin, o)); cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, o));
+                rmin = fminf(rmin, __shfl_xor_sync(0xffffffffu, rmin, o)); rmax = fmaxf(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
+            }
+            if (i == 0) {
+                const float imb = __fadd_rn(__fdiv_rn(cmax, fmaxf(cmin, 1e-8f)), __fdiv_rn(rmax, fmaxf(rmin, 1e-8f)));
+                sm.scal[1] = imb <= sm.scal[0] ? 1.0f : 0.0f;
+                if (imb <= sm.scal[0]) sm.scal[0] = imb;
+            }
         }
         __syncthreads();
         if (i < kSlice && sm.scal[1] != 0.0f) { sm.best_col[i] = sm.cur_col[i]; sm.best_row[i] = sm.cur_row[i]; }
@@ -108,28 +162,32 @@ __device__ void sinkhorn(AppendSmem<D>& sm, int slice, int iters) {
     if (i < kSlice) {
         sm.log_col[i] = sm.log_row[i] = 0.0f;
         sm.cur_col[i] = sm.cur_row[i] = sm.best_col[i] = sm.best_row[i] = 1.0f;
+        sm.rcp_col[i] = sm.rcp_row[i] = 1.0f;
     }
     if (i == 0) sm.scal[0] = 3.402823466e+38f;
     __syncthreads();
     if (iters <= 0) return;
-    if (i < kSlice) { sm.std_col[i] = col_std(i); sm.std_row[i] = row_std(i); }
+    col_std();
+    row_std();
     keep_best();
     for (int it = 0; it < iters; ++it) {
         if (i < kSlice) {
             const float c = fminf(fmaxf(sm.std_col[i], 1e-3f), 1e3f);
             sm.log_col[i] = fminf(fmaxf(__fadd_rn(sm.log_col[i], logf(c)), -0.3f), 10.0f);
             sm.cur_col[i] = expf(sm.log_col[i]);
+            sm.rcp_col[i] = __fdiv_rn(1.0f, sm.cur_col[i]);
         }
         __syncthreads();
-        if (i < kSlice) sm.std_row[i] = row_std(i);
-        __syncthreads();
+        row_std();
         if (i < kSlice) {
             const float r = fminf(fmaxf(sm.std_row[i], 1e-3f), 1e3f);
             sm.log_row[i] = fminf(fmaxf(__fadd_rn(sm.log_row[i], logf(r)), -0.3f), 10.0f);
             sm.cur_row[i] = expf(sm.log_row[i]);
+            sm.rcp_row[i] = __fdiv_rn(1.0f, sm.cur_row[i]);
         }
         __syncthreads();
-        if (i < kSlice) { sm.std_row[i] = row_std(i); sm.std_col[i] = col_std(i); }
+        row_std();
+        col_std();
         keep_best();
     }
 }
@@ -282,21 +340,36 @@ __global__ void __launch_bounds__(kThreads) append_kernel(LayerView L, const uin
                 *reinterpret_cast<const uint4*>(src + static_cast<int64_t>(r) * D + c * 8);
         }
     }
-    // new rows: one warp per row, lane l holds dims l + 32 r
+    // new rows: one warp per row, lane l holds dims l + 32 r.  A warp has up to 16 rows of the tile: it reads them
+    // eight at a time before rotating any, so that it waits for global memory twice, not sixteen times.
     const uint16_t* src = which ? v : k;
-    for (int tt = t.begin + warp; tt < t.end; tt += kThreads / 32) {
-        const int token = t.base + tt - pos0;
-        const uint16_t* row = src + (static_cast<int64_t>(token) * L.kv_heads + head) * D;
-        float val[D / 32];
+    constexpr int kBatch = 8, kWarpsPerCta = kThreads / 32;
+    for (int t0 = t.begin + warp; t0 < t.end; t0 += kBatch * kWarpsPerCta) {
+        uint16_t raw[kBatch][D / 32];
 #pragma unroll
-        for (int r = 0; r < D / 32; ++r) val[r] = in_to_f32<kBf16>(row[lane + 32 * r]);
-        hadamard_warp<D>(val, lane);
-        __half* st = L.stage_row(which, slot, head, tt);
+        for (int u = 0; u < kBatch; ++u) {
+            const int tt = t0 + u * kWarpsPerCta;
+            if (tt < t.end) {
+                const uint16_t* row = src + (static_cast<int64_t>(t.base + tt - pos0) * L.kv_heads + head) * D;
 #pragma unroll
-        for (int r = 0; r < D / 32; ++r) {
-            const __half h = __float2half_rn(val[r]);
-            sm.rows[tt * kStride + lane + 32 * r] = h;
-            if (write_stage) st[lane + 32 * r] = h;
+                for (int r = 0; r < D / 32; ++r) raw[u][r] = row[lane + 32 * r];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int tt = t0 + u * kWarpsPerCta;
+            if (tt >= t.end) break;
+            float val[D / 32];
+#pragma unroll
+            for (int r = 0; r < D / 32; ++r) val[r] = in_to_f32<kBf16>(raw[u][r]);
+            hadamard_warp<D>(val, lane);
+            __half* st = L.stage_row(which, slot, head, tt);
+#pragma unroll
+            for (int r = 0; r < D / 32; ++r) {
+                const __half h = __float2half_rn(val[r]);
+                sm.rows[tt * kStride + lane + 32 * r] = h;
+                if (write_stage) st[lane + 32 * r] = h;
+            }
         }
     }
     if (!seal) return;
