@@ -571,7 +571,7 @@ def run_batch(args):
     # The sequences are independent: dealt over a few streams (longest first) the fixed part of one call -- first
     # requests, merge, the reduce kernel -- runs under the page streaming of the others.  Inside the captured graph
     # the streams become parallel branches.
-    n_streams = max(1, min(args.streams or 4, len(seqs)))
+    n_streams = max(1, min(args.streams or 8, len(seqs)))
     side = [torch.cuda.Stream(device=E.dev) for _ in range(n_streams)]
     lanes = E.pkg.sharded.deal_sequences([n for _, n in seqs], n_streams)
 
@@ -759,7 +759,7 @@ def main():
                     choices=["decode32k", "decodectx", "long379k", "batch32", "verify131k", "prefill262k", "append"],
                     help="decode32k is the contract line; the others are BASELINE configs 4A, 4B, 2 and 3")
     ap.add_argument("--layers", type=int, default=0, help="layers held for long379k / verify131k (default 4)")
-    ap.add_argument("--streams", type=int, default=0, help="batch32: streams the independent sequences are dealt over (default 4)")
+    ap.add_argument("--streams", type=int, default=0, help="batch32: streams the independent sequences are dealt over (default 8)")
     ap.add_argument("--chunk", type=int, default=0, help="append: tokens per append call (default 1024)")
     ap.add_argument("--iters", type=int, default=0, help="append: Sinkhorn iterations of the encoder (0 = bit-exact regime, 16 = engine default)")
     ap.add_argument("--ctx", type=int, default=0, help="context for decodectx (default 131072) / prefix length for prefill262k (default 262144)")

@@ -14,10 +14,10 @@ from .build import build  # noqa: F401
 
 
 def __getattr__(name):
-    if name == "sharded":
+    if name in ("sharded", "dump"):
         import importlib
 
-        return importlib.import_module(__name__ + ".sharded")
+        return importlib.import_module(__name__ + "." + name)
     if name in ("KvarnLayer", "merge_partials", "default_scale", "cache"):
         import importlib
 
