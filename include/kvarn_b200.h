@@ -71,7 +71,7 @@ typedef struct kvb_layer {
 } kvb_layer;
 
 /* bits OR-ed into *error_word */
-enum { KVB_ERR_PAGE_RANGE = 1u, KVB_ERR_TABLE_RANGE = 2u, KVB_ERR_WAIT_TIMEOUT = 4u, KVB_ERR_POSITIONS = 8u };
+enum { KVB_ERR_PAGE_RANGE = 1u, KVB_ERR_TABLE_RANGE = 2u, KVB_ERR_WAIT_TIMEOUT = 4u, KVB_ERR_POSITIONS = 8u, KVB_ERR_GEOMETRY = 16u };
 
 const char* kvb_last_error_string(void);
 int kvb_version(void);
@@ -119,6 +119,20 @@ int kvb_attn_decode(const kvb_layer* layer, const void* q, const int32_t* pos_de
 size_t kvb_static_scratch_bytes(void);
 int kvb_attn_decode_static(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
                            void* out, void* stream);
+
+/* Decode for `batch` (1..64) independent sequences in one pair of launches; larger batches: several calls.
+ * No counterpart in the reference, whose kvarn128 path is single-sequence (patches/0003:1181-1190).
+ * `layers_dev` is a DEVICE array of `batch` kvb_layer structs (upload it once: the descriptors only hold
+ * pointers and sizes), all with the geometry given here (kv_heads, q_heads, head_dim = 128, dtype) and
+ * sinkhorn_iters = 0; an entry that disagrees sets KVB_ERR_GEOMETRY in its error word.  The caches may share
+ * planes (one pool, one block table per sequence) or not.  q, out: [batch][q_heads][head_dim]; pos_dev: [batch]
+ * positions of the newest token of each sequence (device).  kv_len_max: HOST array of upper bounds of the lengths:
+ * it shapes the grid -- every sequence gets splits in proportion to its bound -- and must be the same at capture
+ * and replay.  Workspace: kvb_batch_workspace_bytes(same bounds). */
+size_t kvb_batch_workspace_bytes(const int32_t* kv_len_max, int batch, int kv_heads, int q_heads, int head_dim);
+int kvb_attn_decode_batch(const kvb_layer* layers_dev, int batch, int kv_heads, int q_heads, int head_dim, int dtype,
+                          const void* q, const int32_t* pos_dev, float scale, const int32_t* kv_len_max, void* workspace,
+                          void* out, void* stream);
 
 /* Same, but stops before the final normalisation: writes the log-sum-exp partial of keys
  * [key_begin, key_end) -- part_m[q_heads] (max logit, natural log units), part_l[q_heads] (sum of

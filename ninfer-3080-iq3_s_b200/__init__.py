@@ -18,7 +18,7 @@ def __getattr__(name):
         import importlib
 
         return importlib.import_module(__name__ + "." + name)
-    if name in ("KvarnLayer", "merge_partials", "default_scale", "cache"):
+    if name in ("KvarnLayer", "DecodeBatch", "merge_partials", "default_scale", "cache"):
         import importlib
 
         cache = importlib.import_module(__name__ + ".cache")

@@ -119,6 +119,33 @@ class KvarnLayer:
         return int(self.error_word.item())
 
 
+class DecodeBatch:
+    """kvb_attn_decode_batch over a fixed set of sequences (up to 64): the layer descriptors are uploaded once, the
+    grid is shaped by the host's bounds of the lengths (`kv_len_max`, fixed for the life of the object)."""
+
+    def __init__(self, layers, kv_len_max):
+        lib = capi.load()
+        first = layers[0]
+        assert all((L.head_dim, L.kv_heads, L.q_heads, L.dtype) == (first.head_dim, first.kv_heads, first.q_heads, first.dtype) for L in layers)
+        self.layers, self.n = list(layers), len(layers)
+        self.geo = (first.kv_heads, first.q_heads, first.head_dim, capi.DTYPE_BF16 if first.dtype == torch.bfloat16 else capi.DTYPE_F16)
+        raw = b"".join(bytes(L.c) for L in layers)
+        self.descriptors = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(first.device)
+        self.bounds = (C.c_int32 * self.n)(*[int(x) for x in kv_len_max])
+        nbytes = lib.kvb_batch_workspace_bytes(self.bounds, self.n, first.kv_heads, first.q_heads, first.head_dim)
+        if nbytes == 0:
+            raise ValueError("kvb_batch_workspace_bytes refused the batch: " + lib.kvb_last_error_string().decode())
+        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=first.device)
+
+    def attn_decode(self, q: torch.Tensor, pos: torch.Tensor, scale: float, out=None) -> torch.Tensor:
+        """q: [n, q_heads, head_dim]; pos: int32 [n] on the device -> out [n, q_heads, head_dim]."""
+        out = torch.empty_like(q) if out is None else out
+        kv_heads, q_heads, head_dim, dtype = self.geo
+        capi.check(capi.load().kvb_attn_decode_batch(_ptr(self.descriptors), self.n, kv_heads, q_heads, head_dim, dtype, _ptr(q), _ptr(pos),
+                                                     scale, self.bounds, _ptr(self.workspace), _ptr(out), _stream()))
+        return out
+
+
 def merge_partials(m: torch.Tensor, l: torch.Tensor, o: torch.Tensor, dtype: torch.dtype = torch.float16) -> torch.Tensor:
     """m, l: [parts, q_heads]; o: [parts, q_heads, head_dim] -> [q_heads, head_dim]."""
     parts, qh, d = o.shape

@@ -13,7 +13,7 @@ LIB_PATH = os.environ.get("KVB_LIBRARY", os.path.join(_HERE, "libkvarn_b200.so")
 
 KVB_OK, KVB_EINVAL, KVB_ECUDA, KVB_ERANGE, KVB_ETIMEOUT = range(5)
 DTYPE_F16, DTYPE_BF16 = 0, 1
-ERR_PAGE_RANGE, ERR_TABLE_RANGE, ERR_WAIT_TIMEOUT, ERR_POSITIONS = 1, 2, 4, 8
+ERR_PAGE_RANGE, ERR_TABLE_RANGE, ERR_WAIT_TIMEOUT, ERR_POSITIONS, ERR_GEOMETRY = 1, 2, 4, 8, 16
 
 
 class KvarnError(RuntimeError):
@@ -56,6 +56,9 @@ SYMBOLS = {
     "kvb_merge_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                      C.c_void_p, C.c_void_p]),
     "kvb_merge_partials_packed": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "kvb_batch_workspace_bytes": (C.c_size_t, [C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int]),
+    "kvb_attn_decode_batch": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_float,
+                                        C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_void_p]),
     "kvb_peer_ring_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "kvb_attn_decode_sharded": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p,
                                           C.POINTER(kvb_peer_ring), C.c_void_p, C.c_void_p]),

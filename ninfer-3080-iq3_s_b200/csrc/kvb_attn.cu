@@ -19,7 +19,9 @@
 // fp32 accuracy, and p * scale_V is rounded to fp16 once.  Codes are unpacked with one logic op per pair
 // (see unpack8); V pairs are formed across two keys with a byte permute and the probabilities change from
 // accumulator to operand layout with one movmatrix per 8 keys, so nothing is transposed through memory.
+#include <algorithm>
 #include <climits>
+#include <cstddef>
 
 #include "kvb_common.cuh"
 #include "kvb_ptx.cuh"
@@ -437,15 +439,15 @@ __device__ __forceinline__ void process_stage_group(const __half* krow, const __
     }
 }
 
+// The work of one CTA: split `split` (P.nsplit = the open tile) of KV head `head`, row block `zb`; its partial goes
+// to rows pidx .. pidx + 15 of the workspace.
 template <int NB, bool kOther>
-__global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
+__device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int head, int zb, int64_t pidx) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(smem_raw);
     const LayerView& L = P.L;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.y, zb = blockIdx.z, split = blockIdx.x;
     const int G = L.q_heads / L.kv_heads;
-    grid_dependency_wait();  // q, the positions and the cache come from the kernels before this one
     // ---- order of the first memory requests: the few bytes everything waits for (positions, q rows, page table
     //      entries) go out first, then the first page of every warp, then -- after the rotation of q, about a
     //      microsecond later -- the second page.  At short contexts the whole cache is requested in this first burst:
@@ -645,7 +647,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
     }
     __syncthreads();
     const float* all = reinterpret_cast<const float*>(sm.slots);
-    const int64_t pidx = ((static_cast<int64_t>(head) * gridDim.z + zb) * (P.nsplit + 1) + split) * kRows;
     for (int e = threadIdx.x; e < 8 * NB * (D / 4); e += kThreads) {  // one thread: four dims of one row
         const int row = e / (D / 4), d = 4 * (e % (D / 4));
         float m = -INFINITY;
@@ -667,6 +668,65 @@ __global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
         *reinterpret_cast<float4*>(P.ws_o + (pidx + row) * D + d) = o;
         if (d == 0) { P.ws_m[pidx + row] = m; P.ws_l[pidx + row] = l; }
     }
+}
+
+template <int NB, bool kOther>
+__global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
+    grid_dependency_wait();  // q, the positions and the cache come from the kernels before this one
+    const int head = blockIdx.y, zb = blockIdx.z, split = blockIdx.x;
+    attn_cta<NB, kOther>(P, split, head, zb, ((static_cast<int64_t>(head) * gridDim.z + zb) * (P.nsplit + 1) + split) * kRows);
+}
+
+// Batched decode: `n` independent sequences (their caches described by device-resident kvb_layer structs, same
+// geometry) in one launch.  Sequence b owns parts prefix[b] .. prefix[b + 1] - 1 of the grid's x axis: its splits
+// over sealed pages, then its open tile; the number of splits follows the host's bound of its length, so long and
+// short sequences give CTAs of similar size.
+constexpr int kBatchMax = 64;
+struct BatchPlan {
+    int n;                      // sequences; 0 = not a batched call
+    int prefix[kBatchMax + 1];  // parts before sequence b
+};
+struct BatchParams {
+    const LayerView* layers;  // [n], device memory (layout of kvb_layer)
+    const uint16_t* q;        // [n][q_heads][D]
+    const int32_t* pos;       // [n] position of the newest token of each sequence
+    float scale_log2;
+    float* ws_m;              // [H][total parts][16]
+    float* ws_l;
+    float* ws_o;
+    BatchPlan plan;
+};
+
+__device__ __forceinline__ int batch_entry_of(const BatchPlan& plan, int part) {  // largest b with prefix[b] <= part
+    int lo = 0, hi = plan.n - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (plan.prefix[mid] <= part) lo = mid;
+        else hi = mid - 1;
+    }
+    return lo;
+}
+
+template <int NB>
+__global__ void __launch_bounds__(kThreads, 1) attn_batch_kernel(const BatchParams B) {
+    grid_dependency_wait();
+    const int part = blockIdx.x, head = blockIdx.y;
+    const int b = batch_entry_of(B.plan, part);
+    AttnParams P;
+    P.L = B.layers[b];
+    if ((P.L.head_dim != D || P.L.iters != 0) && threadIdx.x == 0) P.L.flag(KVB_ERR_GEOMETRY);  // results undefined, no fault
+    P.q = B.q + static_cast<int64_t>(b) * P.L.q_heads * D;
+    P.pos = B.pos + b;
+    P.total_pos = B.pos + b;
+    P.T = 1;
+    P.scale_log2 = B.scale_log2;
+    P.nsplit = B.plan.prefix[b + 1] - B.plan.prefix[b] - 1;
+    P.key_begin = 0;
+    P.key_end = INT_MAX;
+    P.ws_m = B.ws_m;
+    P.ws_l = B.ws_l;
+    P.ws_o = B.ws_o;
+    attn_cta<NB, false>(P, part - B.plan.prefix[b], head, 0, (static_cast<int64_t>(head) * gridDim.x + part) * kRows);
 }
 
 // Merge the partials of all splits of one query row, normalise, rotate back (H is its own inverse) and
@@ -707,13 +767,20 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
                                                                   const float* __restrict__ ws_o, int parts, int T, int q_heads,
                                                                   int kv_heads, int zblocks, int dtype, uint16_t* __restrict__ out,
                                                                   float* __restrict__ part_m, float* __restrict__ part_l,
-                                                                  float* __restrict__ part_o, const PushTarget push) {
+                                                                  float* __restrict__ part_o, const PushTarget push,
+                                                                  const BatchPlan plan) {
     __shared__ float4 so[kReduceWarps][32];
     __shared__ float sl[kReduceWarps];
     const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = q_heads / kv_heads, tq = row / q_heads, qh = row % q_heads, head = qh / G, gq = qh % G;
-    const int R = tq * G + gq, zb = R / kRows, r = R % kRows;
-    const int64_t base = (static_cast<int64_t>(head) * zblocks + zb) * parts * kRows + r;
+    int64_t base;
+    if (plan.n > 0) {  // batched decode: row = (sequence tq, q head); the sequence's parts are plan.prefix[tq] ..
+        parts = plan.prefix[tq + 1] - plan.prefix[tq];
+        base = (static_cast<int64_t>(head) * plan.prefix[plan.n] + plan.prefix[tq]) * kRows + gq;
+    } else {
+        const int R = tq * G + gq, zb = R / kRows, r = R % kRows;
+        base = (static_cast<int64_t>(head) * zblocks + zb) * parts * kRows + r;
+    }
     grid_dependency_wait();  // launched while the attention kernel still runs: its partials are complete from here on
     launch_dependents();
     // the number of this call on the ring (read early: its latency hides behind the partial loads)
@@ -995,7 +1062,7 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     const int total_rows = T * layer->q_heads;
     KVB_CUDA_OK(launch_early(reduce_kernel, dim3(total_rows), dim3(kReduceWarps * 32), 0, stream, P.ws_m, P.ws_l, P.ws_o, parts, T,
                              layer->q_heads, layer->kv_heads, Z, layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o,
-                             push != nullptr ? *push : PushTarget{}));
+                             push != nullptr ? *push : PushTarget{}, BatchPlan{}));
     return KVB_OK;
 }
 
@@ -1105,6 +1172,86 @@ extern "C" int kvb_attn_decode_sharded(const kvb_layer* layer, const void* q, co
     push.world = ring->world;
     return launch_attention(layer, q, pos_dev, pos_dev, 1, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr, nullptr,
                             static_cast<cudaStream_t>(stream), "kvb_attn_decode_sharded", &push);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Batched decode of independent sequences.
+namespace kvb {
+namespace {
+
+static_assert(sizeof(LayerView) == sizeof(kvb_layer) && offsetof(LayerView, error_word) == offsetof(kvb_layer, error_word) &&
+                  offsetof(LayerView, table_stride) == offsetof(kvb_layer, table_stride) &&
+                  offsetof(LayerView, iters) == offsetof(kvb_layer, sinkhorn_iters),
+              "the device reads kvb_layer structs as LayerView");
+
+// Parts (splits over sealed pages + the open tile) of every sequence from the host's bounds of their lengths:
+// about eight CTAs per SM in total, at least 16 pages per split, at most 63 splits per sequence.
+int plan_batch(const int32_t* kv_len_max, int batch, int kv_heads, BatchPlan& plan) {
+    int64_t total_pages = 0;
+    for (int b = 0; b < batch; ++b) total_pages += 2 * (kv_len_max[b] / kTile);
+    const int64_t want = std::max<int64_t>(batch, static_cast<int64_t>(8) * sm_count() / kv_heads);
+    const int64_t chunk = std::max<int64_t>(16, (total_pages + want - 1) / want);
+    plan.n = batch;
+    plan.prefix[0] = 0;
+    for (int b = 0; b < batch; ++b) {
+        const int64_t pages = 2 * (kv_len_max[b] / kTile);
+        int nsplit = static_cast<int>((pages + chunk - 1) / chunk);
+        nsplit = std::min(std::max(nsplit, 1), kReduceWarps * kMaxPartsPerWarp - 1);
+        plan.prefix[b + 1] = plan.prefix[b] + nsplit + 1;
+    }
+    return plan.prefix[batch];
+}
+
+}  // namespace
+}  // namespace kvb
+
+extern "C" size_t kvb_batch_workspace_bytes(const int32_t* kv_len_max, int batch, int kv_heads, int q_heads, int head_dim) {
+    using namespace kvb;
+    if (kv_len_max == nullptr || batch < 1 || batch > kBatchMax || kv_heads < 1 || q_heads < kv_heads || head_dim != 128) return 0;
+    for (int b = 0; b < batch; ++b)
+        if (kv_len_max[b] < 1) return 0;
+    BatchPlan plan;
+    const size_t rows = static_cast<size_t>(kv_heads) * plan_batch(kv_len_max, batch, kv_heads, plan) * kRows;
+    return rows * (2 + head_dim) * sizeof(float);
+}
+
+extern "C" int kvb_attn_decode_batch(const kvb_layer* layers_dev, int batch, int kv_heads, int q_heads, int head_dim, int dtype,
+                                     const void* q, const int32_t* pos_dev, float scale, const int32_t* kv_len_max, void* workspace,
+                                     void* out, void* stream) {
+    using namespace kvb;
+    if (layers_dev == nullptr || q == nullptr || pos_dev == nullptr || kv_len_max == nullptr || workspace == nullptr || out == nullptr)
+        return fail(KVB_EINVAL, "kvb_attn_decode_batch: null argument");
+    if (batch < 1 || batch > kBatchMax) return fail(KVB_ERANGE, "kvb_attn_decode_batch: %d sequences (1..%d per call)", batch, kBatchMax);
+    if (head_dim != 128) return fail(KVB_ERANGE, "kvb_attn_decode_batch: head_dim %d (128 supported; other shapes: one kvb_attn_decode per sequence)", head_dim);
+    if (kv_heads < 1 || kv_heads > 8 || q_heads < kv_heads || q_heads % kv_heads != 0 || q_heads / kv_heads > kRows)
+        return fail(KVB_EINVAL, "kvb_attn_decode_batch: %d q heads over %d kv heads", q_heads, kv_heads);
+    if (dtype != KVB_DTYPE_F16 && dtype != KVB_DTYPE_BF16) return fail(KVB_EINVAL, "kvb_attn_decode_batch: dtype %d", dtype);
+    for (int b = 0; b < batch; ++b)
+        if (kv_len_max[b] < 1) return fail(KVB_EINVAL, "kvb_attn_decode_batch: kv_len_max[%d] = %d", b, kv_len_max[b]);
+    BatchParams B;
+    const int total = plan_batch(kv_len_max, batch, kv_heads, B.plan);
+    const size_t rows = static_cast<size_t>(kv_heads) * total * kRows;
+    B.layers = reinterpret_cast<const LayerView*>(layers_dev);
+    B.q = static_cast<const uint16_t*>(q);
+    B.pos = pos_dev;
+    B.scale_log2 = scale * 1.4426950408889634f;
+    B.ws_m = static_cast<float*>(workspace);
+    B.ws_l = B.ws_m + rows;
+    B.ws_o = B.ws_l + rows;
+    const int smem = static_cast<int>(sizeof(AttnSmem));
+    static bool opted = false;
+    if (!opted) {
+        KVB_CUDA_OK(cudaFuncSetAttribute(attn_batch_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        KVB_CUDA_OK(cudaFuncSetAttribute(attn_batch_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        opted = true;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool upper = q_heads / kv_heads > 8;
+    KVB_CUDA_OK(launch_early(upper ? attn_batch_kernel<2> : attn_batch_kernel<1>, dim3(total, kv_heads, 1), dim3(kThreads), smem, st, B));
+    KVB_CUDA_OK(launch_early(reduce_kernel, dim3(batch * q_heads), dim3(kReduceWarps * 32), 0, st, B.ws_m, B.ws_l, B.ws_o, 0, batch, q_heads,
+                             kv_heads, 1, dtype, static_cast<uint16_t*>(out), static_cast<float*>(nullptr), static_cast<float*>(nullptr),
+                             static_cast<float*>(nullptr), PushTarget{}, B.plan));
+    return KVB_OK;
 }
 
 namespace kvb {

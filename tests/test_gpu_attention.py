@@ -329,3 +329,50 @@ def test_sharded_decode_ring_merges_arrived_peers_in_rank_order():
             sent = ring._keep[r].view(torch.int32).view(2, world, block, 2)[call & 1, rank]
             assert torch.equal(sent[:, 0], mine) and bool((sent[:, 1] == call).all()), (call, r)
     assert int(ring.state[0].item()) == 3
+
+
+def test_batched_decode_equals_one_call_per_sequence():
+    """kvb_attn_decode_batch over sequences of very different lengths (shorter than a tile, exactly one tile, long
+    ones) against the oracle, sequence by sequence, and against kvb_attn_decode (same kernels, but the keys are cut
+    into different splits, so the last bits may differ); bounds larger than the true lengths still work."""
+    import torch
+
+    lens = [5, 128, 700, 1100, 64, 3001, 257, 1999]
+    twins = []
+    for i, n in enumerate(lens):
+        tw = Twin(D=128, H=4, QH=24, capacity_tokens=n + 8, seed=400 + i)
+        tw.append(orc.synth_kv(410 + i, n, 4, 128, 1), orc.synth_kv(410 + i, n, 4, 128, 2))
+        twins.append(tw)
+    dev = twins[0].dev
+    scale = 1.0 / np.sqrt(128)
+    qh = np.stack([orc.synth_q(420 + i, 1, 24, 128)[0] for i in range(len(lens))])
+    q = torch.from_numpy(qh).to(dev)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=dev)
+    want = torch.stack([tw.gpu.attn_decode(q[i], pos[i:i + 1], scale, lens[i]) for i, tw in enumerate(twins)])
+    for slack in (0, 4096):
+        batch = pkg().DecodeBatch([tw.gpu for tw in twins], [n + slack for n in lens])
+        out = batch.attn_decode(q, pos, scale)
+        torch.cuda.synchronize()
+        assert (out.float() - want.float()).abs().max().item() <= 2.0 ** -9 * want.float().abs().max().item(), slack
+        for i, tw in enumerate(twins):
+            ref = tw.cpu.attention(qh[i:i + 1], np.array([lens[i] - 1], np.int32), scale, 24, threads=2)
+            ok, msg = attn_close(out[i:i + 1].float().cpu().numpy(), ref)
+            assert ok, f"sequence {i} (slack {slack}): {msg}"
+            assert tw.gpu.errors() == 0
+
+
+def test_batched_decode_refuses_bad_arguments():
+    import ctypes as C
+
+    capi = pkg().capi
+    lib = capi.load()
+    bounds = (C.c_int32 * 2)(100, 0)
+    assert lib.kvb_batch_workspace_bytes(bounds, 2, 4, 24, 128) == 0          # a bound of zero
+    bounds = (C.c_int32 * 2)(100, 100)
+    assert lib.kvb_batch_workspace_bytes(bounds, 2, 4, 24, 256) == 0          # head_dim 256: one call per sequence
+    assert lib.kvb_batch_workspace_bytes(bounds, 2, 4, 24, 128) > 0
+    fake = C.c_void_p(256)
+    st = lib.kvb_attn_decode_batch(fake, 65, 4, 24, 128, 0, fake, fake, 0.1, bounds, fake, fake, None)
+    assert st == capi.KVB_ERANGE
+    st = lib.kvb_attn_decode_batch(fake, 2, 4, 24, 128, 0, fake, fake, 0.1, bounds, None, fake, None)
+    assert st == capi.KVB_EINVAL
