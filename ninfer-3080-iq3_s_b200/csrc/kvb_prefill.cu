@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     const int t1 = static_cast<int>(static_cast<int64_t>(ntiles) * (zs + 1) / P.ksplit);
     const int32_t* tbl = L.table();
     const uint32_t idesc_qk = tc::idesc_f16(kM, kN, false, false), idesc_pv = tc::idesc_f16(kM, D, false, true);
-    const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), p_addr = k_addr;
+    const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v);
 
     float m_run = -INFINITY, l_run = 0.0f;
     bool have_o = false, failed = false;
@@ -210,15 +210,15 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
             sm.ks[dim_slot(tid)] = cur.ks;
             sm.kz[dim_slot(tid)] = cur.kz;
         }
-        // ---- the previous P V reads P from the K/P buffer and V from its own: it must have drained first
-        if (have_o && !mbar_wait_bounded(&sm.bar_o, (it - 1) & 1)) { failed = true; }
         __syncthreads();  // scale tables visible; nobody still reads the previous tile's tables
-        // ---- K tile -> shared memory, then S = Q K^T on the tensor cores
+        // ---- K tile -> shared memory (the previous P V does not touch the K buffer: P lives in tensor memory)
         if (sealed) {
             dequant_row<true>(cur.codes, sm.k, tid, sm, 0, 0);
         } else {
             stage_row_to_tile(L.stage_row(0, t & 1, head, tid), sm.k, tid, base + tid < kv_total);
         }
+        // ---- the previous P V reads P from the columns S = Q K^T is about to overwrite, and the V buffer: drain it
+        if (have_o && !mbar_wait_bounded(&sm.bar_o, (it - 1) & 1)) { failed = true; }
         fence_proxy_async();
         __syncthreads();
         if (tid == 0) {
@@ -265,14 +265,20 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         const bool moved = have_o && m_new > m_run;
         m_run = m_new;
         float sum = 0.0f;
+        // P stays in tensor memory: fp16 pairs over the first 64 columns of S (already in registers), the A operand
+        // of the P V product -- no shared-memory round trip for P
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-            float p[8];
+        for (int c = 0; c < 2; ++c) {
+            uint32_t pk[32];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { p[j] = fast_exp2(s[8 * c + j] - m_use); sum += p[j]; }
-            *reinterpret_cast<uint4*>(sm.k + tile_off(tid, 8 * c)) =
-                make_uint4(pack_half2(p[0], p[1]), pack_half2(p[2], p[3]), pack_half2(p[4], p[5]), pack_half2(p[6], p[7]));
+            for (int j = 0; j < 32; ++j) {
+                const float p0 = fast_exp2(s[64 * c + 2 * j] - m_use), p1 = fast_exp2(s[64 * c + 2 * j + 1] - m_use);
+                sum += p0 + p1;
+                pk[j] = pack_half2(p0, p1);
+            }
+            tc::tmem_st32(tmem_s + lane_base + 32 * c, pk);
         }
+        tc::tmem_st_wait();
         l_run = l_run * alpha + sum;
         if (__any_sync(0xffffffffu, moved)) {  // rescale this warp's 32 rows of O (alpha = 1 for rows that did not move)
 #pragma unroll
@@ -295,9 +301,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
             tc::fence_after_sync();
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
-                const uint32_t po = (kk >> 2) * 16384 + (kk & 3) * 32;  // 16 keys along K of the P tile
-                tc::mma_f16_ss(tmem_o, tc::smem_desc(p_addr + po, 16, 1024), tc::smem_desc(v_addr + kk * 2048, 16384, 1024), idesc_pv,
-                               have_o || kk > 0);
+                tc::mma_f16_ts(tmem_o, tmem_s + 8 * kk, tc::smem_desc(v_addr + kk * 2048, 16384, 1024), idesc_pv, have_o || kk > 0);  // 16 keys = 8 columns of P
             }
             tc::commit(&sm.bar_o);
         }
