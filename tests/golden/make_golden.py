@@ -8,6 +8,8 @@ Fixtures written (all derived from data files of the reference, no source code):
                   (Sinkhorn iterations 0): input tile (already fp16-exact, stored as fp16) and the
                   full record bytes the reference oracle produced for it.
   gvk2_it16.npz   4 records of .../real_k4v4.bin (16 iterations) with the reference's s_col/s_row.
+  gvk2_v2.npz     4 two-bit V records of .../real_k4v2.bin (16 iterations): the bit-string packing at a width
+                  other than 4.
   p1_slot_map_k4v4.csv   the K4V4 rows of kvarn-evidence/offsets-g128/out/p1_slot_map_g128.csv
                   (plane, page_row, col, item, slice, index): the slot of every axis entry in a
                   scale page at head_dim 256.
@@ -65,6 +67,12 @@ def main():
                         records=np.stack([r["rec"] for r in pick]),
                         s_col=np.stack([r["s_col"] for r in pick]), s_row=np.stack([r["s_row"] for r in pick]),
                         best_iter=np.array([r["best_iter"] for r in pick]))
+    v2 = read_gvk2(os.path.join(ev, "verify-g128/data/real_k4v2.bin"))
+    pick = [r for r in v2 if r["name"] in ("L35_v_h0_s0_g0", "L35_v_h3_s1_g0", "L63_v_h1_s0_g0", "L63_v_h2_s1_g0")]
+    assert len(pick) == 4 and all(r["bits"] == 2 for r in pick)
+    np.savez_compressed(os.path.join(HERE, "gvk2_v2.npz"), names=np.array([r["name"] for r in pick]),
+                        tiles=np.stack([r["tile"].astype(np.float16) for r in pick]),
+                        records=np.stack([r["rec"] for r in pick]), iters=np.array([r["iters"] for r in pick]))
     with open(os.path.join(ev, "offsets-g128/out/p1_slot_map_g128.csv")) as f, \
             open(os.path.join(HERE, "p1_slot_map_k4v4.csv"), "w", newline="") as g:
         w = csv.writer(g)

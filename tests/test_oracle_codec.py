@@ -43,6 +43,18 @@ def test_golden_records_iters16(oracle):
         assert np.array_equal(got, rec), name
 
 
+def test_golden_two_bit_records(oracle):
+    """The reference's K4V2 tier: 2-bit V records (bit string, four codes per byte, low bits first), 16 iterations."""
+    g = np.load(os.path.join(GOLDEN, "gvk2_v2.npz"))
+    for name, tile, rec, iters in zip(g["names"], g["tiles"], g["records"], g["iters"]):
+        got, q, _, _ = oracle.quantize_tile(tile.astype(np.float32), 2, int(iters))
+        assert got.size == 128 * 128 * 2 // 8 + 384 * 2
+        assert np.array_equal(got, rec), name
+        flat = q.reshape(-1)
+        assert flat.max() <= 3
+        assert np.array_equal(flat[0::4] | (flat[1::4] << 2) | (flat[2::4] << 4) | (flat[3::4] << 6), rec[:4096])
+
+
 def test_dequant_roundtrip_quality(oracle):
     g = np.load(os.path.join(GOLDEN, "gvk2_it0.npz"))
     tile = g["tiles"][0].astype(np.float32)
@@ -108,6 +120,15 @@ def test_port_equals_compiled_reference(oracle):
             rrec, rbc, rbr, _ = oracle.ref_quantize_tile(t, 4, iters)
             assert np.array_equal(rec, rrec) and np.array_equal(bc, rbc) and np.array_equal(br, rbr)
             assert np.array_equal(oracle.dequant_tile(rec, 128, 128), oracle.ref_dequant_tile(rrec, 128, 128))
+    # the other widths of the reference's tier table (bit-string packing across byte boundaries for 3, 5, 6)
+    t = rng.standard_normal((128, 128)).astype(np.float16).astype(np.float32)
+    for bits in (2, 3, 5, 6, 8):
+        for iters in (0, 16):
+            rec, q, bc, br = oracle.quantize_tile(t, bits, iters)
+            rrec, rbc, rbr, _ = oracle.ref_quantize_tile(t, bits, iters)
+            assert rec.size == 128 * 128 * bits // 8 + 768 and np.array_equal(rec, rrec), (bits, iters)
+            assert q.max() <= (1 << bits) - 1
+            assert np.array_equal(oracle.dequant_tile(rec, 128, 128, bits), oracle.ref_dequant_tile(rrec, 128, 128, bits))
     xs = rng.standard_normal(5000).astype(np.float32) * 1e-6
     for x in xs:
         assert oracle.lib().kvo_f32_to_f16(float(x)) == oracle.ref().bee_ref_f32_to_f16(float(x))
