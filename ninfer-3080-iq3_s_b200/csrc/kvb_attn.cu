@@ -188,9 +188,9 @@ __device__ __forceinline__ void build_qint(const AttnSmem& sm, const uint8_t* sc
             for (int part = 0; part < 2; ++part)
 #pragma unroll
                 for (int r = 0; r < 2; ++r) {  // b0: local dims 16 kb + 2j + part, b1: +8
-                    const int i0 = 16 * kb + 8 * r + part;
-                    f.b[nb][kb][part][0][r] = (hi[i0] & 255) | ((hi[i0 + 2] & 255) << 8) | ((hi[i0 + 4] & 255) << 16) | ((hi[i0 + 6] & 255) << 24);
-                    f.b[nb][kb][part][1][r] = (lo[i0] & 255) | ((lo[i0 + 2] & 255) << 8) | ((lo[i0 + 4] & 255) << 16) | ((lo[i0 + 6] & 255) << 24);
+                    const int i0 = 16 * kb + 8 * r + part;  // low bytes of four digits -> one word: three byte permutes
+                    f.b[nb][kb][part][0][r] = prmt(prmt(hi[i0], hi[i0 + 2], 0x0040), prmt(hi[i0 + 4], hi[i0 + 6], 0x0040), 0x5410);
+                    f.b[nb][kb][part][1][r] = prmt(prmt(lo[i0], lo[i0 + 2], 0x0040), prmt(lo[i0 + 4], lo[i0 + 6], 0x0040), 0x5410);
                 }
     }
 }
