@@ -502,8 +502,18 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
         const int n = max(pe - pb, 0);
         const int c0 = pb + static_cast<int>(static_cast<int64_t>(n) * split / P.nsplit);
         const int c1 = pb + static_cast<int>(static_cast<int64_t>(n) * (split + 1) / P.nsplit);
-        w0 = c0 + (c1 - c0) * warp / kWarps;
-        w1 = c0 + (c1 - c0) * (warp + 1) / kWarps;
+        // A warp that starts in the middle of a tile pays the per-tile set-up (scale transpose, q digits) for two
+        // tiles where one would do: around one or two tiles per warp, warps take whole tiles (measured: 6 % faster at
+        // 32,768 tokens; with longer ranges the extra set-up no longer shows and page granularity balances better).
+        const int u0 = c0 >> 1, u1 = (c1 + 1) >> 1;  // tiles the CTA touches
+        if (u1 - u0 >= kWarps - 1 && u1 - u0 <= 2 * kWarps) {
+            w0 = max(c0, 2 * (u0 + (u1 - u0) * warp / kWarps));
+            w1 = min(c1, 2 * (u0 + (u1 - u0) * (warp + 1) / kWarps));
+            if (w1 < w0) w1 = w0;
+        } else {
+            w0 = c0 + (c1 - c0) * warp / kWarps;
+            w1 = c0 + (c1 - c0) * (warp + 1) / kWarps;
+        }
         ids_base = w0;
         ids = load_ids(w0);
         ids_next = load_ids(w0 + 32);
