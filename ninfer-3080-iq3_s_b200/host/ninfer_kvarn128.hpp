@@ -127,4 +127,30 @@ inline void causal_attention_prompt_launch(const void* q, const void* k, const v
                   "causal_attention_prompt");
 }
 
+// ---- calls without a counterpart in the reference (one GPU, one sequence per call there)
+
+// Decode for up to 64 independent sequences in one call.  `layers_dev`: device array of kvb_layer descriptors (upload
+// once); `kv_len_max`: host array of upper bounds of the lengths; q, out: [batch][q_heads][head_dim]; pos: [batch].
+inline std::size_t causal_attention_batch_workspace_bytes_kvarn128(const std::int32_t* kv_len_max, int batch, int kv_heads,
+                                                                  const Kvarn128Geometry& geo = {}) {
+    return kvb_batch_workspace_bytes(kv_len_max, batch, kv_heads, geo.q_heads, geo.head_dim);
+}
+inline void causal_attention_cached_small_t_batch_launch(const kvb_layer* layers_dev, int batch, int kv_heads, const void* q,
+                                                         const std::int32_t* pos, float scale, const std::int32_t* kv_len_max,
+                                                         void* workspace, void* out, cudaStream_t stream,
+                                                         const Kvarn128Geometry& geo = {}) {
+    detail::raise(kvb_attn_decode_batch(layers_dev, batch, kv_heads, geo.q_heads, geo.head_dim, geo.dtype, q, pos, scale, kv_len_max,
+                                        workspace, out, stream),
+                  "causal_attention_cached_small_t_batch");
+}
+
+// Decode of one sequence whose tile ranges live on several GPUs: this rank's range in `view`, partials exchanged by
+// the kernels through the peer-mapped ring buffers of `ring` (see kvb_peer_ring in the C header).
+inline void causal_attention_cached_small_t_sharded_launch(const void* q, const std::int32_t* local_pos, float scale,
+                                                           const Kvarn128LayerView& view, const kvb_peer_ring& ring, void* workspace,
+                                                           void* out, cudaStream_t stream) {
+    detail::raise(kvb_attn_decode_sharded(&view.layer, q, local_pos, scale, view.kv_len_max, workspace, &ring, out, stream),
+                  "causal_attention_cached_small_t_sharded");
+}
+
 }  // namespace ninfer::ops

@@ -45,6 +45,18 @@ int main() {
     view.kv_len_max = 32768;
     if (causal_attention_split_capacity_kvarn128(view, 1) < 2) { std::printf("FAIL: split capacity\n"); ++failures; }
     if (causal_attention_workspace_bytes_kvarn128(view, 1) == 0) { std::printf("FAIL: workspace bytes\n"); ++failures; }
+    // batched decode: more than 64 sequences per call are refused before anything is launched
+    {
+        std::int32_t bounds[2] = {100, 100};
+        if (causal_attention_batch_workspace_bytes_kvarn128(bounds, 2, 4, geo) == 0) { std::printf("FAIL: batch workspace bytes\n"); ++failures; }
+        try {
+            causal_attention_cached_small_t_batch_launch(reinterpret_cast<const kvb_layer*>(fake), 65, 4, fake, reinterpret_cast<const std::int32_t*>(fake),
+                                                         0.1f, bounds, fake, fake, nullptr, geo);
+            std::printf("FAIL: 65 sequences accepted\n");
+            ++failures;
+        } catch (const std::invalid_argument&) {
+        }
+    }
     if (kvarn128_stage_slots() != 2) { std::printf("FAIL: stage slots\n"); ++failures; }
     std::printf(failures ? "host mirror: %d failure(s)\n" : "host mirror: ok\n", failures);
     return failures;
