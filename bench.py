@@ -25,7 +25,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 D, H, QH, LAYERS, CTX = 128, 4, 24, 16, 32768
-TRAFFIC_BYTES_PER_TOKEN = 597.4
+TRAFFIC_BYTES_PER_TOKEN = 602.3
 SEALED_B, TAIL_B = 140, 512  # algorithmic bytes per sealed / open-tile token per KV head (codes + 12 B of axes | fp16 K+V rows)
 
 
