@@ -171,7 +171,8 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     // Everything a tile needs from global memory before its K side can be de-quantised; fetched one tile ahead
     // so that the page-table lookup and the load latency hide behind the previous tile's softmax.
     struct KFetch {
-        uint4 codes[4];
+        uint4 codes[4], vcodes[4];
+        uint32_t vsz;
         __half ks, kz;
         int32_t page;  // page of this thread's key (-1: tile unusable)
         bool sealed, ok;
@@ -187,6 +188,10 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         const uint4* kc = reinterpret_cast<const uint4*>(L.k_code + page_head_offset(64, L.kv_heads, f.page, head) + (tid & 63) * 64);
 #pragma unroll
         for (int i = 0; i < 4; ++i) f.codes[i] = kc[i];
+        const uint4* vc = reinterpret_cast<const uint4*>(L.v_code + page_head_offset(64, L.kv_heads, f.page, head) + (tid & 63) * 64);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f.vcodes[i] = vc[i];
+        f.vsz = *reinterpret_cast<const uint32_t*>(L.v_scale + page_head_offset(4, L.kv_heads, f.page, head) + (tid & 63) * 4 + 2);
         // per-dim scale / zero point of the tile (stored in both pages): page row d/2 = [s s z z other]
         const __half* ksp = L.k_scale + page_head_offset(5, L.kv_heads, pg0, head);
         f.ks = ksp[(tid >> 1) * 5 + (tid & 1)];
@@ -199,14 +204,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         const int base = t * kN;
         const bool sealed = cur.sealed;
         if (!cur.ok) { fetch_k(t + 1, nxt); continue; }
-        // V side of this tile: issue the loads now, use them after the K side
-        uint4 vcodes[4];
-        uint32_t vsz = 0;
         if (sealed) {
-            const uint4* vc = reinterpret_cast<const uint4*>(L.v_code + page_head_offset(64, L.kv_heads, cur.page, head) + (tid & 63) * 64);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) vcodes[i] = vc[i];
-            vsz = *reinterpret_cast<const uint32_t*>(L.v_scale + page_head_offset(4, L.kv_heads, cur.page, head) + (tid & 63) * 4 + 2);
             sm.ks[dim_slot(tid)] = cur.ks;
             sm.kz[dim_slot(tid)] = cur.kz;
         }
@@ -232,11 +230,11 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         }
         // ---- V tile -> shared memory (overlaps the QK MMA), then start fetching the next tile
         if (sealed) {
-            dequant_row<false>(vcodes, sm.v, tid, sm, prmt(vsz, vsz, 0x1010), prmt(vsz, vsz, 0x3232));
+            dequant_row<false>(cur.vcodes, sm.v, tid, sm, prmt(cur.vsz, cur.vsz, 0x1010), prmt(cur.vsz, cur.vsz, 0x3232));
         } else {
             stage_row_to_tile(L.stage_row(1, t & 1, head, tid), sm.v, tid, base + tid < kv_total);
         }
-        fetch_k(t + 1, nxt);
+        fetch_k(t + 1, nxt);  // (issuing this at the top of the step was measured slower)
         // ---- softmax of row `tid`
         if (!mbar_wait_bounded(&sm.bar_s, it & 1)) { failed = true; }
         if (__syncthreads_or(failed)) { failed = true; break; }
