@@ -199,16 +199,19 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     };
     KFetch cur, nxt;
     fetch_k(t0, nxt);
+    bool tables_ready = false;  // the scale tables of this tile were written during the previous step (saves a barrier)
     for (int t = t0; t < t1; ++t) {
         cur = nxt;
         const int base = t * kN;
         const bool sealed = cur.sealed;
-        if (!cur.ok) { fetch_k(t + 1, nxt); continue; }
-        if (sealed) {
-            sm.ks[dim_slot(tid)] = cur.ks;
-            sm.kz[dim_slot(tid)] = cur.kz;
+        if (!cur.ok) { fetch_k(t + 1, nxt); tables_ready = false; continue; }
+        if (!tables_ready) {
+            if (sealed) {
+                sm.ks[dim_slot(tid)] = cur.ks;
+                sm.kz[dim_slot(tid)] = cur.kz;
+            }
+            __syncthreads();  // scale tables visible
         }
-        __syncthreads();  // scale tables visible; nobody still reads the previous tile's tables
         // ---- K tile -> shared memory (the previous P V does not touch the K buffer: P lives in tensor memory)
         if (sealed) {
             dequant_row<true>(cur.codes, sm.k, tid, sm, 0, 0);
@@ -291,6 +294,12 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
             tc::tmem_st_wait();
         }
         }  // warp_has_rows (rows of the other warps are never read: their P and O may hold anything)
+        // the scale tables of the next tile: this tile's K rows were de-quantised two barriers ago
+        tables_ready = nxt.ok;
+        if (nxt.ok && nxt.sealed) {
+            sm.ks[dim_slot(tid)] = nxt.ks;
+            sm.kz[dim_slot(tid)] = nxt.kz;
+        }
         // ---- O += P V
         fence_proxy_async();
         tc::fence_before_sync();
