@@ -239,8 +239,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         }
         fetch_k(t + 1, nxt);  // (issuing this at the top of the step was measured slower)
         // ---- softmax of row `tid`
-        if (!mbar_wait_bounded(&sm.bar_s, it & 1)) { failed = true; }
-        if (__syncthreads_or(failed)) { failed = true; break; }
+        if (!mbar_wait_bounded(&sm.bar_s, it & 1)) { failed = true; }  // a warp that gave up reads stale S; the CTA agrees below
         tc::fence_after_sync();
         if (warp_has_rows) {
         float s[kN];
@@ -300,10 +299,10 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
             sm.ks[dim_slot(tid)] = nxt.ks;
             sm.kz[dim_slot(tid)] = nxt.kz;
         }
-        // ---- O += P V
+        // ---- O += P V (every warp has its V rows in shared memory and its P rows in tensor memory; any failed wait ends the walk)
         fence_proxy_async();
         tc::fence_before_sync();
-        __syncthreads();
+        if (__syncthreads_or(failed)) { failed = true; break; }
         if (tid == 0) {
             tc::fence_after_sync();
 #pragma unroll
