@@ -542,7 +542,7 @@ def run_decode_ctx(args):
         "config": {"workload": f"decode_attention_only_ctx{ctx}", "layers": layers_n, "q_heads": QH, "kv_heads": H, "head_dim": D,
                    "l2": f"{layers_n} layers x {ctx * H * 146 / 1e6:.0f} MB between revisits"},
         "roofline": {"bound": "hbm", "achieved": nbytes / (us * 1e-6) / 1e9, "peak": peak, "peak_kind": kind, "unit": "GB/s",
-                     "frac": nbytes / (us * 1e-6) / 1e9 / peak, "traffic": TRAFFIC_BYTES_PER_TOKEN * ctx},
+                     "frac": nbytes / (us * 1e-6) / 1e9 / peak, "traffic": TRAFFIC_BYTES_PER_TOKEN * ctx if D == 128 else None},
         "graph_captured": graphed, "clocks": clk.summary(), "gpu_launches": args.steps * layers_n * 2,
     })
 
@@ -664,7 +664,7 @@ def run_append(args):
     tiles, tail = T // 128, T % 128
     # rows read + planes written for the sealed tiles + stage rows written for the open tail (and, as the reference
     # keeps them for roll-back, for the last sealed tile)
-    nbytes = 2 * T * H * D * 2 + tiles * 128 * H * 146 + (tail + (128 if tiles else 0)) * H * D * 2 * 2
+    nbytes = 2 * T * H * D * 2 + tiles * 128 * H * 146 * (D // 128) + (tail + (128 if tiles else 0)) * H * D * 2 * 2
     us = ms * 1e3 / layers_n
     E.finish({
         "metric": "append_hbm_gbs", "value": nbytes / (us * 1e-6) / 1e9, "unit": "GB/s", "n_gpus": E.world, "steps": args.steps,
@@ -779,8 +779,15 @@ def main():
     ap.add_argument("--streams", type=int, default=0, help="batch32: streams the independent sequences are dealt over (default 8)")
     ap.add_argument("--chunk", type=int, default=0, help="append: tokens per append call (default 1024)")
     ap.add_argument("--iters", type=int, default=0, help="append: Sinkhorn iterations of the encoder (0 = bit-exact regime, 16 = engine default)")
+    ap.add_argument("--head-dim", type=int, default=128, choices=[128, 256],
+                    help="decodectx / append: 256 is the reference engine's own geometry (runs on the general kernels)")
     ap.add_argument("--ctx", type=int, default=0, help="context for decodectx (default 131072) / prefix length for prefill262k (default 262144)")
     args = ap.parse_args()
+    if args.head_dim != 128:
+        if args.workload not in ("decodectx", "append") or args.impl != "b200":
+            ap.error("--head-dim 256 is for --workload decodectx / append")
+        global D, SEALED_B, TAIL_B
+        D, SEALED_B, TAIL_B = 256, 280, 1024
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "decode32k":
