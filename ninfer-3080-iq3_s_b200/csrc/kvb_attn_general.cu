@@ -4,6 +4,8 @@
 // points; a plain CUDA-core kernel: one CTA per (key range, KV head, query token), one warp per key, every
 // element de-quantised as (q * scale_axis + zp_axis) * other_axis in fp32 (reference kvarn128_codec.cuh:331-347),
 // fp32 dot products with warp-shuffle reductions, running softmax per warp, log-sum-exp merges at the end.
+// Lane l owns the contiguous dims R l .. R l + R - 1 (R = head_dim / 32): its codes of a key are one 16- or 32-bit
+// word, its per-dim factors stay in registers for a page, its query values for the whole call.
 #include <climits>
 
 #include "kvb_common.cuh"
@@ -27,7 +29,6 @@ struct GeneralParams {
 
 template <int DD> struct GeneralSmem {
     float q[kMaxG][DD];        // rotated, scaled query rows of this KV head
-    float k_scale[DD], k_zp[DD], v_other[DD];
     float wm[kGWarps][kMaxG], wl[kGWarps][kMaxG];
     float wo[kGWarps][kMaxG][DD];
 };
@@ -64,13 +65,19 @@ __global__ void __launch_bounds__(kGThreads) general_attn_kernel(const GeneralPa
 #pragma unroll
         for (int j = 0; j < R; ++j) o[g][j] = 0.0f;
     }
+    __syncthreads();
+    float qr[kMaxG][R];  // this lane's dims of the query rows
+#pragma unroll
+    for (int g = 0; g < kMaxG; ++g)
+#pragma unroll
+        for (int j = 0; j < R; ++j) qr[g][j] = g < G ? sm.q[g][R * lane + j] : 0.0f;
     auto attend = [&](const float (&kv)[R], const float (&vv)[R]) {  // one key against the G query rows
 #pragma unroll
         for (int g = 0; g < kMaxG; ++g) {
             if (g >= G) break;
             float dot = 0.0f;
 #pragma unroll
-            for (int j = 0; j < R; ++j) dot = fmaf(sm.q[g][lane + 32 * j], kv[j], dot);
+            for (int j = 0; j < R; ++j) dot = fmaf(qr[g][j], kv[j], dot);
 #pragma unroll
             for (int sft = 16; sft > 0; sft >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, sft);
             const float mn = fmaxf(m[g], dot), a = __expf(m[g] - mn), p = __expf(dot - mn);
@@ -94,29 +101,46 @@ __global__ void __launch_bounds__(kGThreads) general_attn_kernel(const GeneralPa
         if (page < 0) continue;
         const __half* ks = L.k_scale + page_head_offset(Geo_::kKScaleLeading, L.kv_heads, page, head);
         const __half* vs = L.v_scale + page_head_offset(Geo_::kVScaleLeading, L.kv_heads, page, head);
-        __syncthreads();  // previous page's tables no longer in use
-        for (int d = threadIdx.x; d < DD; d += kGThreads) {
-            sm.k_scale[d] = __half2float(ks[Geo_::kKScaleLeading * (d / c) + d % c]);
-            sm.k_zp[d] = __half2float(ks[Geo_::kKScaleLeading * (d / c) + c + d % c]);
-            sm.v_other[d] = __half2float(vs[Geo_::kVScaleLeading * (d / c) + d % c]);
+        float ksc[R], kzp[R], vot[R];  // per-dim factors of the tile for this lane's dims (the same in both pages)
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            const int d = R * lane + j;
+            ksc[j] = __half2float(ks[Geo_::kKScaleLeading * (d / c) + d % c]);
+            kzp[j] = __half2float(ks[Geo_::kKScaleLeading * (d / c) + c + d % c]);
+            vot[j] = __half2float(vs[Geo_::kVScaleLeading * (d / c) + d % c]);
         }
-        __syncthreads();
+        const int s = (R * lane) / kSlice;  // the slice this lane's dims lie in
         const uint8_t* kc = L.k_code + page_head_offset(Geo_::kCodeLeading, L.kv_heads, page, head);
         const uint8_t* vc = L.v_code + page_head_offset(Geo_::kCodeLeading, L.kv_heads, page, head);
-        for (int off = warp; off < kPage; off += kGWarps) {
-            const int p = lp * kPage + off;
+        // the warp's eight keys of the page: every load is issued before the first key is used
+        constexpr int kKeys = kPage / kGWarps;
+        uint32_t wk[kKeys], wv[kKeys];  // R codes of 4 bits, dim R lane + j at bits 4 j
+        __half ko[kKeys], vsa[kKeys], vzp[kKeys];
+#pragma unroll
+        for (int u = 0; u < kKeys; ++u) {
+            const int off = warp + kGWarps * u;
+            if constexpr (R == 8) {
+                wk[u] = *reinterpret_cast<const uint32_t*>(kc + off * Geo_::kCodeLeading + 4 * lane);
+                wv[u] = *reinterpret_cast<const uint32_t*>(vc + off * Geo_::kCodeLeading + 4 * lane);
+            } else {
+                wk[u] = *reinterpret_cast<const uint16_t*>(kc + off * Geo_::kCodeLeading + 2 * lane);
+                wv[u] = *reinterpret_cast<const uint16_t*>(vc + off * Geo_::kCodeLeading + 2 * lane);
+            }
+            ko[u] = ks[Geo_::kKScaleLeading * off + 2 * c + s];
+            vsa[u] = vs[Geo_::kVScaleLeading * off + c + s];
+            vzp[u] = vs[Geo_::kVScaleLeading * off + c + S + s];
+        }
+#pragma unroll
+        for (int u = 0; u < kKeys; ++u) {
+            const int p = lp * kPage + warp + kGWarps * u;
             if (p < key_begin || p >= key_end) continue;  // warp-uniform
+            const float kof = __half2float(ko[u]), vsf = __half2float(vsa[u]), vzf = __half2float(vzp[u]);
             float kv[R], vv[R];
 #pragma unroll
             for (int j = 0; j < R; ++j) {
-                const int d = lane + 32 * j, s = d / kSlice, sh = (d & 1) * 4;
-                const float qk = static_cast<float>((kc[off * Geo_::kCodeLeading + d / 2] >> sh) & 15);
-                const float qv = static_cast<float>((vc[off * Geo_::kCodeLeading + d / 2] >> sh) & 15);
-                const float ko = __half2float(ks[Geo_::kKScaleLeading * off + 2 * c + s]);
-                const float vsa = __half2float(vs[Geo_::kVScaleLeading * off + c + s]);
-                const float vzp = __half2float(vs[Geo_::kVScaleLeading * off + c + S + s]);
-                kv[j] = __fmul_rn(__fadd_rn(__fmul_rn(qk, sm.k_scale[d]), sm.k_zp[d]), ko);
-                vv[j] = __fmul_rn(__fadd_rn(__fmul_rn(qv, vsa), vzp), sm.v_other[d]);
+                const float qk = static_cast<float>((wk[u] >> (4 * j)) & 15u), qv = static_cast<float>((wv[u] >> (4 * j)) & 15u);
+                kv[j] = __fmul_rn(__fadd_rn(__fmul_rn(qk, ksc[j]), kzp[j]), kof);
+                vv[j] = __fmul_rn(__fadd_rn(__fmul_rn(qv, vsf), vzf), vot[j]);
             }
             attend(kv, vv);
         }
@@ -130,7 +154,7 @@ __global__ void __launch_bounds__(kGThreads) general_attn_kernel(const GeneralPa
             const __half* vr = L.stage_row(1, tile & 1, head, tt);
             float kv[R], vv[R];
 #pragma unroll
-            for (int j = 0; j < R; ++j) { kv[j] = __half2float(kr[lane + 32 * j]); vv[j] = __half2float(vr[lane + 32 * j]); }
+            for (int j = 0; j < R; ++j) { kv[j] = __half2float(kr[R * lane + j]); vv[j] = __half2float(vr[R * lane + j]); }
             attend(kv, vv);
         }
     }
@@ -141,7 +165,7 @@ __global__ void __launch_bounds__(kGThreads) general_attn_kernel(const GeneralPa
         if (g >= G) break;
         if (lane == 0) { sm.wm[warp][g] = m[g]; sm.wl[warp][g] = l[g]; }
 #pragma unroll
-        for (int j = 0; j < R; ++j) sm.wo[warp][g][lane + 32 * j] = o[g][j];
+        for (int j = 0; j < R; ++j) sm.wo[warp][g][R * lane + j] = o[g][j];
     }
     __syncthreads();
     const int64_t base = ((static_cast<int64_t>(tq) * L.kv_heads + head) * P.nsplit + split) * G;
@@ -205,7 +229,7 @@ int general_splits(int kv_len_max, int T) {
     if (T > 8) return 1;  // a chunk already brings one CTA per token and head
     const int pages = kv_len_max / kPage;
     int n = pages / 8;
-    return n < 1 ? 1 : (n > 32 ? 32 : n);
+    return n < 1 ? 1 : (n > 36 ? 36 : n);  // with four KV heads: one CTA per SM of a 148-SM part
 }
 
 template <int DD>
