@@ -41,6 +41,13 @@ def append_bytes(tokens: int) -> int:
     return 2 * tokens * H * D * 2 * 2
 
 
+def shuffled_table(seed: int, logical_pages: int, physical_pages: int):
+    """A seeded page table: logical page -> distinct physical page (the pages of a sequence are scattered)."""
+    import numpy as np
+
+    return np.random.default_rng([seed, 99]).permutation(physical_pages)[:logical_pages].astype(np.int32)
+
+
 class ClockSampler:
     """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
 
@@ -189,7 +196,7 @@ def run_gpu(args):
 
     layers = []
     for li in range(LAYERS):
-        table = torch.from_numpy(orc.shuffled_table(100 * rank + li, lp, lp))
+        table = torch.from_numpy(shuffled_table(100 * rank + li, lp, lp))
         L = pkg.KvarnLayer(D, H, QH, lp, table, device=str(dev))
         for c0 in range(0, CTX, 4096):  # prefill by appends
             L.append(synth(4096, H), synth(4096, H), torch.arange(c0, c0 + 4096, dtype=torch.int32, device=dev))
@@ -351,12 +358,10 @@ class _Env:
 
     def layer(self, tokens, room, seed):
         """A layer pre-filled with `tokens` synthetic tokens and room for `room` more."""
-        from oracle import kvarn_oracle as orc
-
         torch = self.torch
         lp = (tokens + room + 63) // 64 + 2
         lp += lp & 1
-        L = self.pkg.KvarnLayer(D, H, QH, lp, torch.from_numpy(orc.shuffled_table(seed, lp, lp)), device=str(self.dev))
+        L = self.pkg.KvarnLayer(D, H, QH, lp, torch.from_numpy(shuffled_table(seed, lp, lp)), device=str(self.dev))
         for c0 in range(0, tokens, 8192):
             n = min(8192, tokens - c0)
             L.append(self.synth(n, H), self.synth(n, H), torch.arange(c0, c0 + n, dtype=torch.int32, device=self.dev))
@@ -640,11 +645,9 @@ def run_append(args):
     torch = E.torch
     T = args.chunk or 1024
     layers_n = args.layers or max(4, min(64, int(300e6 // (T * H * D * 2 * 2)) + 1))
-    from oracle import kvarn_oracle as orc
-
     lp = (T + 63) // 64 + 2
     lp += lp & 1
-    layers = [E.pkg.KvarnLayer(D, H, QH, lp, torch.from_numpy(orc.shuffled_table(i, lp, lp)), sinkhorn_iters=args.iters, device=str(E.dev))
+    layers = [E.pkg.KvarnLayer(D, H, QH, lp, torch.from_numpy(shuffled_table(i, lp, lp)), sinkhorn_iters=args.iters, device=str(E.dev))
               for i in range(layers_n)]
     k = [E.synth(T, H) for _ in range(layers_n)]
     v = [E.synth(T, H) for _ in range(layers_n)]
