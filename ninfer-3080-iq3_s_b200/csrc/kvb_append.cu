@@ -455,11 +455,10 @@ __global__ void __launch_bounds__(kThreads) decode_tile_kernel(LayerView L, int 
 template <int D, bool kBf16>
 int launch_append(const LayerView& V, const void* k, const void* v, const int32_t* positions, int tokens,
                   cudaStream_t stream) {
-    static bool opted = false;  // per template instance; setting the attribute again is harmless
+    static unsigned long long opted = 0;  // per template instance; setting the attribute again is harmless
     const int smem = static_cast<int>(sizeof(AppendSmem<D>));
-    if (!opted) {
+    if (first_call_on_device(opted)) {
         KVB_CUDA_OK(cudaFuncSetAttribute(append_kernel<D, kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        opted = true;
     }
     const dim3 grid(tokens / kTile + 2, V.kv_heads, 2);
     append_kernel<D, kBf16><<<grid, kThreads, smem, stream>>>(V, static_cast<const uint16_t*>(k),

@@ -987,16 +987,7 @@ __global__ void __launch_bounds__(128) merge_kernel(const float* __restrict__ pm
         out[static_cast<int64_t>(row) * DD + lane + 32 * j] = dtype == KVB_DTYPE_BF16 ? f32_to_out<true>(o[j]) : f32_to_out<false>(o[j]);
 }
 
-int g_sm_count = 0;
-int sm_count() {
-    if (g_sm_count == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-            g_sm_count <= 0)
-            g_sm_count = 148;  // B200
-    }
-    return g_sm_count;
-}
+int sm_count() { return device_sm_count(); }
 
 int zblocks_of(int q_heads, int kv_heads, int rows) { return (rows * (q_heads / kv_heads) + kRows - 1) / kRows; }
 
@@ -1061,11 +1052,10 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     P.ws_o = P.ws_l + rows;
     const bool upper = T * (layer->q_heads / layer->kv_heads) > 8;
     const int smem = static_cast<int>(sizeof(AttnSmem));
-    static bool opted = false;
-    if (!opted) {
+    static unsigned long long opted = 0;
+    if (first_call_on_device(opted)) {
         KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        opted = true;
     }
     const dim3 grid(parts, layer->kv_heads, Z);
     KVB_CUDA_OK(launch_early(upper ? attn_kernel<2, false> : attn_kernel<1, false>, grid, dim3(kThreads), smem, stream, P));
@@ -1250,11 +1240,10 @@ extern "C" int kvb_attn_decode_batch(const kvb_layer* layers_dev, int batch, int
     B.ws_l = B.ws_m + rows;
     B.ws_o = B.ws_l + rows;
     const int smem = static_cast<int>(sizeof(AttnSmem));
-    static bool opted = false;
-    if (!opted) {
+    static unsigned long long opted = 0;
+    if (first_call_on_device(opted)) {
         KVB_CUDA_OK(cudaFuncSetAttribute(attn_batch_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         KVB_CUDA_OK(cudaFuncSetAttribute(attn_batch_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        opted = true;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool upper = q_heads / kv_heads > 8;

@@ -235,10 +235,9 @@ int general_splits(int kv_len_max, int T) {
 template <int DD>
 int launch_general_t(const kvb_layer* layer, const GeneralParams& P, void* out, float* pm, float* pl, float* po, cudaStream_t s) {
     const int smem = static_cast<int>(sizeof(GeneralSmem<DD>));
-    static bool opted = false;
-    if (!opted) {
+    static unsigned long long opted = 0;
+    if (first_call_on_device(opted)) {
         KVB_CUDA_OK(cudaFuncSetAttribute(general_attn_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        opted = true;
     }
     general_attn_kernel<DD><<<dim3(P.nsplit, layer->kv_heads, P.T), kGThreads, smem, s>>>(P);
     KVB_CUDA_OK(cudaGetLastError());

@@ -92,6 +92,27 @@ inline cudaError_t launch_early(void (*kernel)(KArgs...), dim3 grid, dim3 block,
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// True the first time it is called on the current device for this `seen` mask: for set-up CUDA keeps per device
+// (the opt-in to large dynamic shared memory).  Not synchronised -- two threads making the first call at once
+// both do the set-up, which is harmless.
+inline bool first_call_on_device(unsigned long long& seen) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return true;
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (seen & bit) return false;
+    seen |= bit;
+    return true;
+}
+// SM count of the current device (cached per device; 148 if the query fails).
+inline int device_sm_count() {
+    static int cache[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    int& n = cache[dev & 63];
+    if (n <= 0 && (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)) n = 148;
+    return n;
+}
+
 LayerView make_view(const kvb_layer& L);
 int check_layer(const kvb_layer* L, const char* who);
 

@@ -394,14 +394,7 @@ __global__ void __launch_bounds__(256) prefill_merge_kernel(const float* __restr
         out[static_cast<int64_t>(row) * D + lane + 32 * j] = dtype == KVB_DTYPE_BF16 ? f32_to_out<true>(o[j]) : f32_to_out<false>(o[j]);
 }
 
-int prefill_sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    }
-    return n;
-}
+int prefill_sm_count() { return device_sm_count(); }
 
 void prefill_shape(int kv_len_max, int kv_heads, int q_heads, int tokens, int* mtiles, int* ksplit) {
     const int rows = tokens * (q_heads / kv_heads);
@@ -453,10 +446,9 @@ int launch_chunk_attention(const kvb_layer* layer, const void* q, const int32_t*
     P.ws_l = P.ws_m + rows;
     P.ws_o = P.ws_l + rows;
     const int smem = static_cast<int>(sizeof(PrefillSmem)) + 1024;  // room to align the tiles to 1024 bytes
-    static bool opted = false;
-    if (!opted) {
+    static unsigned long long opted = 0;
+    if (first_call_on_device(opted)) {
         KVB_CUDA_OK(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        opted = true;
     }
     prefill_kernel<<<dim3(P.mtiles, layer->kv_heads, P.ksplit), kThreads, smem, s>>>(P);
     KVB_CUDA_OK(cudaGetLastError());
