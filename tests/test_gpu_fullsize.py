@@ -1,0 +1,116 @@
+"""Size-independent properties at the full size of BASELINE config 4A (one sequence of 378,944 tokens, 24 / 4 heads,
+head_dim 128), where the CPU oracle would take minutes per call:
+  * the planes do not depend on how the tokens were chunked into appends, nor on where the pages lie: two caches
+    with different page tables, filled in chunks of 8,192 and of 4,099 tokens, hold the same bytes page for page;
+  * decode attention is bit-identical on the two caches (same logical content, different physical placement);
+  * the partials of eight tile-aligned key ranges merge to the full result (log-sum-exp associativity);
+  * a looser host bound of the length (kv_len_max) changes the split grid but not the result beyond tolerance.
+"""
+import numpy as np
+import pytest
+
+from helpers import pkg
+
+pytestmark = pytest.mark.gpu
+
+T, D, H, QH = 378_944, 128, 4, 24
+
+
+def _fill(layer, k, v, chunk, dev):
+    import torch
+
+    for c0 in range(0, T, chunk):
+        n = min(chunk, T - c0)
+        layer.append(k[c0:c0 + n], v[c0:c0 + n], torch.arange(c0, c0 + n, dtype=torch.int32, device=dev))
+
+
+def test_config_4a_properties():
+    import torch
+
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4242)
+    k = torch.randn((T, H, D), generator=gen, device=dev, dtype=torch.float32)
+    k[..., [3, 17, 64, 101]] *= 20.0
+    k = k.to(torch.float16)
+    v = torch.randn((T, H, D), generator=gen, device=dev, dtype=torch.float32).to(torch.float16)
+    q = torch.randn((QH, D), generator=gen, device=dev, dtype=torch.float32).to(torch.float16)
+    lp = (T + 63) // 64 + 2
+    lp += lp & 1
+    rng = np.random.default_rng(7)
+    tables = [torch.from_numpy(rng.permutation(lp + 5)[:lp].astype(np.int32)) for _ in range(2)]
+    A = pkg().KvarnLayer(D, H, QH, lp + 5, tables[0], device="cuda:0")
+    B = pkg().KvarnLayer(D, H, QH, lp + 5, tables[1], device="cuda:0")
+    _fill(A, k, v, 8192, dev)
+    _fill(B, k, v, 4099, dev)
+    torch.cuda.synchronize()
+    assert A.errors() == 0 and B.errors() == 0
+    # same bytes, logical page for logical page
+    sealed_pages = 2 * (T // 128)
+    ta, tb = tables[0][:sealed_pages].to(dev).long(), tables[1][:sealed_pages].to(dev).long()
+    for name in ("k_code", "v_code", "k_scale", "v_scale"):
+        assert torch.equal(getattr(A, name)[ta], getattr(B, name)[tb]), name
+    # the open tile (64 tokens of tile 2960, stage slot 0) lives in the stage, identically; rows beyond it are stale
+    # rows of earlier tiles, whose content depends on the chunking and is never read
+    open_tile, live = T // 128, T % 128
+    sa, sb = A.stage.view(2, 2, H, 128, D), B.stage.view(2, 2, H, 128, D)
+    assert live == 64 and torch.equal(sa[:, open_tile & 1, :, :live], sb[:, open_tile & 1, :, :live])
+    pos = torch.tensor([T - 1], dtype=torch.int32, device=dev)
+    scale = 1.0 / np.sqrt(D)
+    full_a = A.attn_decode(q, pos, scale, T)
+    full_b = B.attn_decode(q, pos, scale, T)
+    torch.cuda.synchronize()
+    assert torch.isfinite(full_a.float()).all()
+    assert torch.equal(full_a, full_b)
+    # eight tile-aligned key ranges -> partials -> merge
+    tiles = (T + 127) // 128
+    ms, ls, os_ = [], [], []
+    for r in range(8):
+        b, e = 128 * (tiles * r // 8), min(T, 128 * (tiles * (r + 1) // 8))
+        m, l, o = A.attn_decode_partial(q, pos, scale, T, key_begin=b, key_end=e)
+        ms.append(m.clone()); ls.append(l.clone()); os_.append(o.clone())
+    merged = pkg().cache.merge_partials(torch.stack(ms), torch.stack(ls), torch.stack(os_))
+    ref = full_a.float()
+    tol = 2.0 ** -10 * ref.abs().max().item()
+    assert (merged.float() - ref).abs().max().item() <= tol
+    # a looser bound of the length: other splits, same answer
+    loose = A.attn_decode(q, pos, scale, T + 50_000)
+    assert (loose.float() - ref).abs().max().item() <= tol
+    assert A.errors() == 0
+
+
+def test_config_3_chunk_rows_equal_single_row_decodes():
+    """BASELINE config 3 at full size (1,024-token chunk over a 262,144-token prefix): every row of a causal chunk
+    attention is the decode attention of that row alone over the keys it may see.  Rows 0, 500 and 1,023 of the
+    tensor-core chunk kernel against the warp-level decode kernel on the same cache (two independent kernels),
+    within the chunk kernel's tolerance."""
+    import torch
+
+    prefix, chunk = 262_144, 1024
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(99)
+
+    def rows(n, heads):
+        x = torch.randn((n, heads, D), generator=gen, device=dev, dtype=torch.float32)
+        x[..., [3, 17, 64, 101]] *= 20.0
+        return x.to(torch.float16)
+
+    lp = (prefix + chunk + 63) // 64 + 2
+    lp += lp & 1
+    table = torch.from_numpy(np.random.default_rng(3).permutation(lp).astype(np.int32))
+    L = pkg().KvarnLayer(D, H, QH, lp, table, device="cuda:0")
+    for c0 in range(0, prefix, 8192):
+        L.append(rows(8192, H), rows(8192, H), torch.arange(c0, c0 + 8192, dtype=torch.int32, device=dev))
+    q, k, v = rows(chunk, QH), rows(chunk, H), rows(chunk, H)
+    pos = torch.arange(prefix, prefix + chunk, dtype=torch.int32, device=dev)
+    scale = 1.0 / np.sqrt(D)
+    out = L.attn_prefill(q, k, v, pos, scale, prefix + chunk)
+    torch.cuda.synchronize()
+    assert L.errors() == 0 and torch.isfinite(out.float()).all()
+    for i in (0, 500, chunk - 1):
+        ref = L.attn_decode(q[i], pos[i:i + 1], scale, prefix + chunk).float()
+        got = out[i].float()
+        assert (got - ref).abs().max().item() <= 2.0 ** -8 * ref.abs().max().item(), i
+        assert ((got - ref).norm() / ref.norm()).item() <= 5e-3, i
+    assert L.errors() == 0
