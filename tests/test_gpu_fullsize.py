@@ -114,3 +114,80 @@ def test_config_3_chunk_rows_equal_single_row_decodes():
         assert (got - ref).abs().max().item() <= 2.0 ** -8 * ref.abs().max().item(), i
         assert ((got - ref).norm() / ref.norm()).item() <= 5e-3, i
     assert L.errors() == 0
+
+
+def test_config_2_verify_rows_equal_single_row_decodes():
+    """BASELINE config 2 at full size (131,072-token prefix, 4 and 8 draft rows): row i of a verify step equals the
+    decode of row i alone; width 4 runs on the warp-level kernel, width 8 on the tensor-core chunk kernel.  The
+    second step re-appends at the same positions (the drafts of the first were rolled back)."""
+    import torch
+
+    prefix = 131_072
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+
+    def rows(n, heads):
+        x = torch.randn((n, heads, D), generator=gen, device=dev, dtype=torch.float32)
+        x[..., [3, 17, 64, 101]] *= 20.0
+        return x.to(torch.float16)
+
+    lp = (prefix + 8 + 63) // 64 + 2
+    lp += lp & 1
+    L = pkg().KvarnLayer(D, H, QH, lp, torch.from_numpy(np.random.default_rng(4).permutation(lp).astype(np.int32)), device="cuda:0")
+    for c0 in range(0, prefix, 8192):
+        L.append(rows(8192, H), rows(8192, H), torch.arange(c0, c0 + 8192, dtype=torch.int32, device=dev))
+    scale = 1.0 / np.sqrt(D)
+    for width in (4, 8):
+        q, k, v = rows(width, QH), rows(width, H), rows(width, H)
+        pos = torch.arange(prefix, prefix + width, dtype=torch.int32, device=dev)
+        out = L.attn_verify(q, k, v, pos, scale, prefix + 8)
+        torch.cuda.synchronize()
+        for i in range(width):
+            ref = L.attn_decode(q[i], pos[i:i + 1], scale, prefix + 8).float()
+            got = out[i].float()
+            assert (got - ref).abs().max().item() <= 2.0 ** -8 * ref.abs().max().item(), (width, i)
+            assert ((got - ref).norm() / ref.norm()).item() <= 5e-3, (width, i)
+    assert L.errors() == 0
+
+
+def test_config_4b_batched_decode_equals_one_call_per_sequence():
+    """BASELINE config 4B at full size: 32 sequences of 16,384 .. 131,072 tokens, one kvb_attn_decode_batch call
+    against one kvb_attn_decode per sequence (same kernels, different cuts of the keys)."""
+    import random
+
+    import torch
+
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(6)
+    rnd = random.Random(0)
+    lengths = [rnd.randint(16384, 131072) for _ in range(32)]
+    pool_k = torch.randn((131072 + 4096, H, D), generator=gen, device=dev, dtype=torch.float32).to(torch.float16)
+    pool_v = torch.randn((131072 + 4096, H, D), generator=gen, device=dev, dtype=torch.float32).to(torch.float16)
+    layers = []
+    for i, n in enumerate(lengths):
+        lp = (n + 63) // 64 + 2
+        lp += lp & 1
+        L = pkg().KvarnLayer(D, H, QH, lp, torch.from_numpy(np.random.default_rng(100 + i).permutation(lp).astype(np.int32)), device="cuda:0")
+        shift = 17 * i  # every sequence reads the pool at its own offset: different content per sequence
+        for c0 in range(0, n, 8192):
+            m = min(8192, n - c0)
+            L.append(pool_k[shift + c0:shift + c0 + m], pool_v[shift + c0:shift + c0 + m], torch.arange(c0, c0 + m, dtype=torch.int32, device=dev))
+        layers.append(L)
+    q = torch.randn((32, QH, D), generator=gen, device=dev, dtype=torch.float32).to(torch.float16)
+    pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=dev)
+    scale = 1.0 / np.sqrt(D)
+    want = torch.stack([L.attn_decode(q[i], pos[i:i + 1], scale, lengths[i]) for i, L in enumerate(layers)]).float()
+    out = pkg().DecodeBatch(layers, lengths).attn_decode(q, pos, scale).float()
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all()
+    # The two differ by more than summation order: the weights p * scale_V are rounded to fp16 relative to the running
+    # maximum at the time, which depends on where the keys were cut, and that rounding noise is common to all dims of
+    # a head (it shows up in dim 0 after the inverse rotation).  An output here is the average of 10^5 random values,
+    # about 0.02, so the noise is judged against the scale of V itself: below 2^-13 of the largest |V|.
+    vmax = pool_v.float().abs().max().item()
+    for i in range(32):
+        assert (out[i] - want[i]).abs().max().item() <= 2.0 ** -13 * vmax, i
+        assert ((out[i] - want[i]).norm() / want[i].norm()).item() <= 5e-3, i
+    assert all(L.errors() == 0 for L in layers)
