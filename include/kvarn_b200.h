@@ -184,12 +184,34 @@ int kvb_attn_decode_sharded(const kvb_layer* layer, const void* q, const int32_t
 int kvb_attn_verify(const kvb_layer* layer, const void* q, const void* k, const void* v, const int32_t* positions_dev,
                     int width, float scale, int kv_len_max, void* workspace, void* out, void* stream);
 
+/* The attention half of a verify step alone: causal attention of `rows` (1..8) query tokens whose K/V rows are already
+ * in the cache.  *total_pos_dev is the position of the newest token the cache holds (it decides which tile is the open
+ * one), positions_dev[i] the position of query row i (it sees keys 0..positions[i]).  For the reference's column-block
+ * form of causal_attention_small_t_launch (P3:3508-3545: the whole step is appended when column_begin == 0, the
+ * blocks column_begin > 0 attend only).  Workspace as for kvb_attn_verify. */
+int kvb_attn_rows(const kvb_layer* layer, const void* q, const int32_t* positions_dev, int rows, const int32_t* total_pos_dev,
+                  float scale, int kv_len_max, void* workspace, void* out, void* stream);
+
 /* Prefill chunk: quantise-append `tokens` rows, then causal attention of the chunk over prefix + chunk.
  * q, out: [tokens][q_heads][head_dim].  Replaces causal_attention_prompt_launch (P3:2362-2416). */
 int kvb_attn_prefill(const kvb_layer* layer, const void* q, const void* k, const void* v,
                      const int32_t* positions_dev, int tokens, float scale, int kv_len_max, void* workspace,
                      void* out, void* stream);
 size_t kvb_prefill_workspace_bytes(int kv_len_max, int kv_heads, int q_heads, int head_dim, int tokens);
+
+/* Verify steps and prefill chunks over a sequence whose tile ranges live on several GPUs: causal attention of `tokens`
+ * query rows over THIS cache alone, stopped before the normalisation -- part_m[tokens * q_heads] (max logit, natural
+ * log), part_l (sum of exp(logit - m)), part_o[tokens * q_heads][head_dim] (rotated domain), fp32, row = token * q_heads
+ * + q head.  Nothing is appended: the rank that owns the open tile calls kvb_append for the new rows first.
+ * positions_dev are in this cache's own coordinates (row i sees keys 0..positions[i]; the last entry also tells the
+ * length of the cache): the owner of the new rows passes their local positions, a rank that holds an earlier range
+ * passes its last position for every row.  The partials of all ranks merge with kvb_merge_partials(_packed), passing
+ * tokens * q_heads as the row count.  Workspace: kvb_workspace_bytes(..., rows = tokens, 1) for tokens <= 8,
+ * kvb_prefill_workspace_bytes(..., tokens) for longer chunks.  No counterpart in the reference (single GPU); the
+ * single-GPU operators it extends are causal_attention_small_t_launch and causal_attention_prompt_launch
+ * (P3:3508-3610, 2362-2416), the merge it feeds repeats their split reduction (P3:3149-3170, 3467-3482). */
+int kvb_attn_chunk_partial(const kvb_layer* layer, const void* q, const int32_t* positions_dev, int tokens, float scale,
+                           int kv_len_max, void* workspace, float* part_m, float* part_l, float* part_o, void* stream);
 
 #ifdef __cplusplus
 }

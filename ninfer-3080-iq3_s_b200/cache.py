@@ -51,7 +51,7 @@ class KvarnLayer:
             dtype=capi.DTYPE_BF16 if dtype == torch.bfloat16 else capi.DTYPE_F16, sinkhorn_iters=sinkhorn_iters,
             error_word=self.error_word.data_ptr())
         self._ws = None
-        self._ws_key = None
+        self._pws = None
 
     # ---- kv_cache_append_kvarn128_launch
     def append(self, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor) -> None:
@@ -66,12 +66,19 @@ class KvarnLayer:
         return ok, ov
 
     def workspace(self, kv_len_max: int, rows: int) -> torch.Tensor:
-        key = (kv_len_max, rows)
-        if self._ws_key != key:
-            n = capi.load().kvb_workspace_bytes(kv_len_max, self.kv_heads, self.q_heads, self.head_dim, rows, 1)
-            self._ws = torch.empty(n // 4, dtype=torch.float32, device=self.device)
-            self._ws_key = key
+        """Scratch for attention calls of up to `rows` query tokens at up to `kv_len_max` keys.  One buffer per
+        layer that only ever grows: a CUDA graph that captured its address stays valid as long as the first call
+        (made before the capture) asked for the largest shape the graph uses."""
+        n = capi.load().kvb_workspace_bytes(kv_len_max, self.kv_heads, self.q_heads, self.head_dim, rows, 1)
+        if self._ws is None or self._ws.numel() * 4 < n:
+            self._ws = torch.empty((n + 3) // 4, dtype=torch.float32, device=self.device)
         return self._ws
+
+    def prefill_workspace(self, kv_len_max: int, tokens: int) -> torch.Tensor:
+        n = capi.load().kvb_prefill_workspace_bytes(kv_len_max, self.kv_heads, self.q_heads, self.head_dim, tokens)
+        if self._pws is None or self._pws.numel() * 4 < n:
+            self._pws = torch.empty((n + 3) // 4, dtype=torch.float32, device=self.device)
+        return self._pws
 
     # ---- causal_attention_cached_small_t_launch
     def attn_decode(self, q: torch.Tensor, pos: torch.Tensor, scale: float, kv_len_max: int, out=None) -> torch.Tensor:
@@ -103,17 +110,28 @@ class KvarnLayer:
         out = torch.empty_like(q) if out is None else out
         w = int(q.shape[0])
         capi.check(capi.load().kvb_attn_verify(C.byref(self.c), _ptr(q), _ptr(k), _ptr(v), _ptr(positions), w, scale,
-                                               kv_len_max, _ptr(self.workspace(kv_len_max, 8)), _ptr(out), _stream()))
+                                               kv_len_max, _ptr(self.workspace(kv_len_max, w)), _ptr(out), _stream()))
         return out
 
     # ---- causal_attention_prompt_launch (quantise-append a chunk + causal chunk attention)
     def attn_prefill(self, q, k, v, positions, scale, kv_len_max, out=None):
         out = torch.empty_like(q) if out is None else out
-        n = capi.load().kvb_prefill_workspace_bytes(kv_len_max, self.kv_heads, self.q_heads, self.head_dim, int(q.shape[0]))
-        ws = torch.empty(n // 4, dtype=torch.float32, device=self.device)
+        ws = self.prefill_workspace(kv_len_max, int(q.shape[0]))
         capi.check(capi.load().kvb_attn_prefill(C.byref(self.c), _ptr(q), _ptr(k), _ptr(v), _ptr(positions),
                                                 int(q.shape[0]), scale, kv_len_max, _ptr(ws), _ptr(out), _stream()))
         return out
+
+    # ---- this cache's share of a verify step / prefill chunk over a range-sharded sequence
+    def attn_chunk_partial_packed(self, q, positions, scale, kv_len_max, packed):
+        """q: [tokens, q_heads, head_dim]; positions: int32 [tokens] in this cache's coordinates.  Writes the partials
+        of the tokens * q_heads rows into `packed`, laid out m[rows] | l[rows] | o[rows, D] (fp32, rows * (D + 2) floats)."""
+        tokens = int(q.shape[0])
+        rows, d = tokens * self.q_heads, self.head_dim
+        ws = self.workspace(kv_len_max, tokens) if tokens <= 8 else self.prefill_workspace(kv_len_max, tokens)
+        base = packed.data_ptr()
+        capi.check(capi.load().kvb_attn_chunk_partial(C.byref(self.c), _ptr(q), _ptr(positions), tokens, scale, kv_len_max, _ptr(ws),
+                                                      C.c_void_p(base), C.c_void_p(base + 4 * rows), C.c_void_p(base + 8 * rows), _stream()))
+        return packed
 
     def errors(self) -> int:
         return int(self.error_word.item())

@@ -64,9 +64,13 @@ SYMBOLS = {
                                           C.POINTER(kvb_peer_ring), C.c_void_p, C.c_void_p]),
     "kvb_attn_verify": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                   C.c_float, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "kvb_attn_rows": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_float, C.c_int, C.c_void_p,
+                                C.c_void_p, C.c_void_p]),
     "kvb_attn_prefill": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                    C.c_float, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "kvb_prefill_workspace_bytes": (C.c_size_t, [C.c_int] * 5),
+    "kvb_attn_chunk_partial": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_void_p,
+                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None

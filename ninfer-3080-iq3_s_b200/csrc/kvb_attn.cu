@@ -1,24 +1,28 @@
 // kvb_attn.cu -- paged split-K attention over the quantised cache for 1..8 query tokens (decode, MTP
 // verify), de-quantisation fused into the QK and PV loops.  head_dim 128.
 //
-// Grid (splits + 1, kv heads, row blocks).  A CTA owns one KV head, one contiguous range of sealed pages
-// and a block of up to 16 GQA-merged query rows (row = token * G + q head within the KV head); the extra
-// CTA in x handles the open tile, whose rows are still un-quantised fp16 in the stage.  Inside a CTA each
-// of the 8 warps streams its own sub-range of pages through a private two-slot shared-memory ring filled
-// by bulk async copies (one mbarrier per slot, four contiguous runs per page: K codes, V codes, K scales,
-// V scales), so warps never synchronise with each other until the final merge.
+// Grid (splits, kv heads, row blocks).  A CTA owns one KV head, one contiguous range of sealed tiles (128
+// tokens = two pages) and a block of up to 16 GQA-merged query rows (row = token * G + q head within the KV
+// head); the last split of a head also reads the open tile, whose rows are still un-quantised fp16 in the
+// stage.  Inside a CTA each of the 12 warps streams its own sub-range of tiles through a private ring of six
+// 2 KB slots in shared memory filled by bulk async copies (one mbarrier per slot).  A tile arrives as a header
+// (the K scale page and the two V scale pages, double-buffered) followed by eight chunks of 32 keys: four of
+// K codes, then four of V codes; a slot is refilled as soon as its chunk has been consumed, so five sixths of
+// a warp's ring are in flight at any time and warps never synchronise with each other until the final merge.
 //
-// Math per page (quantised-domain identities, no per-element de-quantisation):
-//   logit[r][j] = other_K[j] * ( sum_d (q'[r][d] * scale_K[d]) * code_K[j][d]  +  sum_d q'[r][d] * zp_K[d] )
-//   o[r][d]    += other_V[d] * ( sum_j (p[r][j] * scale_V[j]) * code_V[j][d]  +  sum_j p[r][j] * zp_V[j] )
-// with q' = H q * softmax_scale * log2(e).  The two contractions run on the warp-level tensor cores
-// (m16n8k16, fp16 operands, fp32 accumulate) with the KEYS (QK) and the DIMS (PV) on the 16-wide M side and
-// the GQA-merged query rows on the 8-wide N side, so six query heads waste a quarter of a tile, not five
-// eighths: S^T[key][row] = K_codes . (q' scale_K)^T and O^T[dim][row] = V_codes^T . (p scale_V)^T.
-// 4-bit codes are exact in fp16, q' * scale_K is split into an fp16 high and low part so the product keeps
-// fp32 accuracy, and p * scale_V is rounded to fp16 once.  Codes are unpacked with one logic op per pair
-// (see unpack8); V pairs are formed across two keys with a byte permute and the probabilities change from
-// accumulator to operand layout with one movmatrix per 8 keys, so nothing is transposed through memory.
+// Math per tile (quantised-domain identities, no per-element de-quantisation), all on the int8 tensor path:
+//   logit[r][j] = sum_d (q'[r][d] * scale_K[d]) * code_K[j][d]  +  sum_d q'[r][d] * zp_K[d]
+//   o[r][d]    += sum_j (p[r][j] * scale_V[j]) * code_V[j][d]   +  sum_j p[r][j] * zp_V[j]
+// with q' = H q * softmax_scale * log2(e).  Both contractions are mma.sync m16n8k32 (u8 x s8/u8 -> s32) with
+// the KEYS (QK) and the DIMS (PV) on the 16-wide M side and the GQA-merged query rows on the 8-wide N side:
+//   * QK: q' * scale_K is quantised per query row to 16 bits = a signed high and an unsigned low byte; the
+//     packed code bytes feed the MMA as they lie in the page (byte & 0x0F = even dim, byte & 0xF0 = 16 x odd
+//     dim), the four integer partial sums recombine exactly in int32.
+//   * PV: p (relative to the row maximum of THIS tile, so p <= 1) times scale_V is quantised to 16 bits = two
+//     unsigned bytes; V codes are transposed to "four keys of one dim per register" by ldmatrix.trans plus one
+//     byte permute and one AND per register; the integer sums of the tile are converted once per tile and
+//     enter the running fp32 accumulators with the weight exp2(tile max - running max).
+// The tile-local reference keeps 16 significant bits below each tile's own maximum, whatever the global one is.
 #include <algorithm>
 #include <climits>
 #include <cstddef>
@@ -30,13 +34,17 @@ namespace kvb {
 namespace {
 
 constexpr int D = 128;
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
-constexpr int kRows = 16;  // query rows per CTA: one or two 8-row N blocks
-constexpr int kKCodeOff = 0, kVCodeOff = 4096, kKScaleOff = 8192, kVScaleOff = 8832, kPageBytes = 9344;
-constexpr int kSlots = 2;
+constexpr int kWarpsDecode = 12;    // warps per CTA for up to 8 merged query rows (one N block per warp)
+constexpr int kWarpsWide = 8;       // ... for 9..16 merged rows (two N blocks per warp: twice the accumulators)
+constexpr int kRows = 16;           // query rows per CTA: one or two 8-row N blocks
+constexpr int kChunkKeys = 32;      // keys per ring slot
+constexpr int kChunkBytes = kChunkKeys * (D / 2);  // 2048: the K or the V codes of 32 keys
+constexpr int kSlots = 6;           // ring slots per warp
+constexpr int kHdrK = 640, kHdrV = 512, kHdrBytes = kHdrK + 2 * kHdrV;  // K scale page (first page of the tile), V scale pages
 constexpr int kScratchBytes = 256 + 256 + 128;  // per warp: scale_K[128], zp_K[128], other_K[64] as fp16
 constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kMagic = 12582912.0f;   // 1.5 * 2^23: x + kMagic has round(x) in its low mantissa bits (|x| < 2^22)
+constexpr float kPMax = 65000.0f;       // largest 16-bit weight (a margin below 65535 absorbs the rounding of the factor)
 
 struct AttnParams {
     LayerView L;
@@ -45,35 +53,40 @@ struct AttnParams {
     const int32_t* total_pos;  // position of the newest token in the cache (kv_total = *total_pos + 1)
     int T;
     float scale_log2;    // softmax scale * log2(e)
-    int nsplit;          // CTAs over sealed pages; blockIdx.x == nsplit is the open-tile CTA
+    int nsplit;          // CTAs over the sealed tiles of a head; the last one also reads the open tile
     int key_begin, key_end;
-    float* ws_m;         // [H][Z][nsplit+1][16]
+    float* ws_m;         // [H][Z][nsplit][16]
     float* ws_l;
-    float* ws_o;         // [H][Z][nsplit+1][16][D]
+    float* ws_o;         // [H][Z][nsplit][16][D]
 };
 
-struct __align__(16) AttnSmem {
-    uint8_t slots[kWarps][kSlots][kPageBytes];
-    uint8_t scratch[kWarps][kScratchBytes];
+struct __align__(128) WarpRing {
+    uint8_t slots[kSlots][kChunkBytes];
+    uint8_t hdr[2][kHdrBytes];
+    uint8_t scratch[kScratchBytes];
+    uint64_t bars[kSlots];
+    uint64_t hbars[2];
+};
+
+template <int W> struct __align__(128) AttnSmem {
+    WarpRing ring[W];
     float4 qfrag[2][8][32];  // q' in per-lane fragment order: [row half][j][lane] = dims 32t+4j..+3 of row g(+8)
-    uint64_t bars[kWarps][kSlots];
     int row_pos[kRows];
 };
 
-// Per-thread state of the running softmax.  Lane (g, t) owns query rows 8 nb + 2t, 2t+1 of n-block nb and,
-// in the PV accumulators, dims 16g .. 16g+15: o[nb][mb] = {(dim 16g+mb, row 2t), (dim 16g+mb, row 2t+1),
-// (dim 16g+8+mb, row 2t), (dim 16g+8+mb, row 2t+1)}.  l and z are partial over the lane's keys.
+// Per-thread state of the running softmax.  Lane (g, t) owns query rows 8 nb + 2t, 2t+1 of n-block nb and dims
+// 32 db + 4g + i (db, i < 4):  o[nb][db][xy][c] is dim 32 db + 4g + xy + 2 (c >> 1), row 8 nb + 2t + (c & 1) -- the
+// accumulator layout of the two MMAs per 32-dim block (xy = 0: even dims, 1: odd dims).  l and z are partial over the
+// lane's keys; everything is relative to the running maximum m (log2 units).
 template <int NB> struct Acc {
-    float o[NB][8][4];
+    float o[NB][4][2][4];
     float m[NB][2], l[NB][2], z[NB][2];
 };
 
-// B fragments of (q' * scale_K)^T per n-block and k-block (b0, b1), high and low fp16 parts, and
-// qz = sum_d q'[row][d] * zp_K[d] for the lane's two rows.
+// B fragments of (q')^T per n-block and k-block (b0, b1), high and low fp16 parts: the open tile's rows are fp16.
 template <int NB> struct QFrag {
     uint32_t hi[NB][8][2];
     uint32_t lo[NB][8][2];
-    float qz[NB][2];
 };
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
@@ -81,73 +94,60 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
     return r;
 }
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_u32(p)));
+}
+// D(16x8, s32) += A(16x32, u8, row) * B(32x8, s8 | u8, col)
+__device__ __forceinline__ void imma_us(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma_uu(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
-// Build the Q-side fragments for one tile from q' (shared memory, fragment order) and the tile's per-dim
-// scale / zero point (warp scratch, natural dim order).  Lane (g, t) prepares row 8 nb + g, dims
-// 32t .. 32t+31.  k-slot pairing follows unpack8: word i of the 32-dim chunk feeds k-blocks 2i (dims
-// +0,+4 | +1,+5) and 2i+1 (dims +2,+6 | +3,+7); un-quantised stage rows use natural pairs (2e, 2e+1).
-template <bool kScaled, int NB>
-__device__ __forceinline__ void build_qfrag(const AttnSmem& sm, const uint8_t* scratch, int lane, QFrag<NB>& f) {
-    const int t = lane & 3;
+// Q-side fragments for the open tile from q' (shared memory, fragment order).  Lane (g, t) prepares row 8 nb + g, dims
+// 32t .. 32t+31 in natural pairs (2e, 2e+1), split into an fp16 high and low part so the product keeps fp32 accuracy.
+template <int NB, typename Smem>
+__device__ __forceinline__ void build_qfrag(const Smem& sm, int lane, QFrag<NB>& f) {
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
-        float qs[32];
-        float qz = 0.0f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float4 qv = sm.qfrag[nb][j][lane];
-            if constexpr (kScaled) {
-                const uint2 ks = *reinterpret_cast<const uint2*>(scratch + (32 * t + 4 * j) * 2);
-                const uint2 kz = *reinterpret_cast<const uint2*>(scratch + 256 + (32 * t + 4 * j) * 2);
-                const float2 s01 = unpack_half2(ks.x), s23 = unpack_half2(ks.y);
-                const float2 z01 = unpack_half2(kz.x), z23 = unpack_half2(kz.y);
-                qs[4 * j + 0] = qv.x * s01.x; qs[4 * j + 1] = qv.y * s01.y;
-                qs[4 * j + 2] = qv.z * s23.x; qs[4 * j + 3] = qv.w * s23.y;
-                qz = fmaf(qv.x, z01.x, qz); qz = fmaf(qv.y, z01.y, qz);
-                qz = fmaf(qv.z, z23.x, qz); qz = fmaf(qv.w, z23.y, qz);
-            } else {
-                qs[4 * j + 0] = qv.x; qs[4 * j + 1] = qv.y; qs[4 * j + 2] = qv.z; qs[4 * j + 3] = qv.w;
-            }
-        }
-        qz += __shfl_xor_sync(0xffffffffu, qz, 1);
-        qz += __shfl_xor_sync(0xffffffffu, qz, 2);  // every lane of group g now holds qz of row 8 nb + g
-        f.qz[nb][0] = __shfl_sync(0xffffffffu, qz, 8 * t);      // row 2t   lives in lanes 4 * (2t) ..
-        f.qz[nb][1] = __shfl_sync(0xffffffffu, qz, 8 * t + 4);  // row 2t+1 lives in lanes 4 * (2t+1) ..
+            const float x[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float x0 = kScaled ? qs[8 * i + e] : qs[8 * i + 2 * e];
-                const float x1 = kScaled ? qs[8 * i + e + 4] : qs[8 * i + 2 * e + 1];
-                const uint32_t h = pack_half2(x0, x1);
-                const float2 hf32 = unpack_half2(h);
-                f.hi[nb][2 * i + (e >> 1)][e & 1] = h;
-                f.lo[nb][2 * i + (e >> 1)][e & 1] = pack_half2(x0 - hf32.x, x1 - hf32.y);
+            for (int h = 0; h < 2; ++h) {  // dims 4j + 2h, +1 of the lane's 32: B register h of 16-dim k-block j
+                const uint32_t hi = pack_half2(x[2 * h], x[2 * h + 1]);
+                const float2 hf = unpack_half2(hi);
+                f.hi[nb][j][h] = hi;
+                f.lo[nb][j][h] = pack_half2(x[2 * h] - hf.x, x[2 * h + 1] - hf.y);
             }
         }
     }
 }
 
 // Integer form of (q' * scale_K)^T for the quantised pages: each row is scaled to 16-bit integers
-// (row scale f = max|.| / 32639) and split into two signed 8-bit digits, Qi = 256 hi + lo, so that the key side
-// can feed its packed code bytes to the int8 tensor path without unpacking nibbles: with L = byte & 0x0F (even
-// dim) and H = byte & 0xF0 (16 x odd dim),   sum_d Qi[d] code[d] = sum_b Qi[2b] L_b + (1/16) sum_b Qi[2b+1] H_b.
-// b[nb][kb][part][digit] holds the B fragments (b0, b1) of 32-byte k-block kb: part 0 = even dims, 1 = odd dims.
+// (row scale f = max|.| / 32639), Qi = 256 hi + lo with hi = Qi >> 8 signed and lo = Qi & 255 unsigned, so that the
+// key side can feed its packed code bytes to the int8 tensor path without unpacking nibbles: with L = byte & 0x0F
+// (even dim) and H = byte & 0xF0 (16 x odd dim),   sum_d Qi[d] code[d] = sum_b Qi[2b] L_b + (1/16) sum_b Qi[2b+1] H_b.
+// b[nb][kb][part][digit] holds the B fragments (b0, b1) of 32-byte k-block kb: part 0 = even dims, 1 = odd dims;
+// digit 0 = high (s8), 1 = low (u8).  The two bytes are read straight out of the float kMagic + Qi.
 template <int NB> struct QInt {
     uint32_t b[NB][2][2][2][2];
     float f[NB][2];   // row scale / 16 of the lane's rows 2t, 2t+1
     float qz[NB][2];  // sum_d q'[row][d] * zp_K[d]
 };
 
-__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-template <int NB>
-__device__ __forceinline__ void build_qint(const AttnSmem& sm, const uint8_t* scratch, int lane, QInt<NB>& f) {
+template <int NB, typename Smem>
+__device__ __forceinline__ void build_qint(const Smem& sm, const uint8_t* scratch, int lane, QInt<NB>& f) {
     const int t = lane & 3;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
@@ -170,27 +170,24 @@ __device__ __forceinline__ void build_qint(const AttnSmem& sm, const uint8_t* sc
         qz += __shfl_xor_sync(0xffffffffu, qz, 2);  // every lane of group g now holds qz of row 8 nb + g
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        const float fr = amax > 0.0f ? amax * (1.0f / 32639.0f) : 1.0f, inv = amax > 0.0f ? 32639.0f / amax : 0.0f;  // 32639 keeps the high digit within [-127, 127]
+        const float fr = amax > 0.0f ? amax * (1.0f / 32639.0f) : 1.0f, inv = amax > 0.0f ? 32639.0f / amax : 0.0f;
         f.qz[nb][0] = __shfl_sync(0xffffffffu, qz, 8 * t);      // row 2t   lives in lanes 4 * (2t) ..
         f.qz[nb][1] = __shfl_sync(0xffffffffu, qz, 8 * t + 4);  // row 2t+1 lives in lanes 4 * (2t+1) ..
         f.f[nb][0] = __shfl_sync(0xffffffffu, fr, 8 * t) * 0.0625f;
         f.f[nb][1] = __shfl_sync(0xffffffffu, fr, 8 * t + 4) * 0.0625f;
-        int hi[32], lo[32];
+        uint32_t x[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const int qi = __float2int_rn(qs[i] * inv);
-            hi[i] = (qi + 128) >> 8;
-            lo[i] = qi - (hi[i] << 8);
-        }
+        for (int i = 0; i < 32; ++i) x[i] = __float_as_uint(fmaf(qs[i], inv, kMagic));  // low 16 bits: Qi (two's complement)
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
             for (int part = 0; part < 2; ++part)
 #pragma unroll
                 for (int r = 0; r < 2; ++r) {  // b0: local dims 16 kb + 2j + part, b1: +8
-                    const int i0 = 16 * kb + 8 * r + part;  // low bytes of four digits -> one word: three byte permutes
-                    f.b[nb][kb][part][0][r] = prmt(prmt(hi[i0], hi[i0 + 2], 0x0040), prmt(hi[i0 + 4], hi[i0 + 6], 0x0040), 0x5410);
-                    f.b[nb][kb][part][1][r] = prmt(prmt(lo[i0], lo[i0 + 2], 0x0040), prmt(lo[i0 + 4], lo[i0 + 6], 0x0040), 0x5410);
+                    const int i0 = 16 * kb + 8 * r + part;
+                    const uint32_t t01 = prmt(x[i0], x[i0 + 2], 0x5140), t23 = prmt(x[i0 + 4], x[i0 + 6], 0x5140);  // [lo lo hi hi]
+                    f.b[nb][kb][part][1][r] = prmt(t01, t23, 0x5410);
+                    f.b[nb][kb][part][0][r] = prmt(t01, t23, 0x7632);
                 }
     }
 }
@@ -206,165 +203,19 @@ __device__ __forceinline__ void transpose_k_scale(const uint8_t* kscale_page, ui
     *reinterpret_cast<uint32_t*>(scratch + 512 + 4 * lane) = prmt(w2, w4, 0x7610);
 }
 
-// Online-softmax update of NG groups of 16 keys whose logits (log2 units) sit in s[nb][grp][4]:
-// {(key g, row 2t), (key g, row 2t+1), (key g+8, row 2t), (key g+8, row 2t+1)} of group grp.
-// On return s holds p = exp2(logit - m_new); acc is rescaled if a row maximum moved.
-template <int NB, int NG>
-__device__ __forceinline__ void softmax_block(float (&s)[NB][NG][4], Acc<NB>& acc) {
-    float muse[NB][2], alpha[NB][2];
-    bool moved = false;
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            float mx = -INFINITY;
-#pragma unroll
-            for (int grp = 0; grp < NG; ++grp) mx = fmaxf(mx, fmaxf(s[nb][grp][j], s[nb][grp][2 + j]));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-            const float mnew = fmaxf(acc.m[nb][j], mx);
-            moved |= mnew > acc.m[nb][j];
-            muse[nb][j] = mnew == -INFINITY ? 0.0f : mnew;
-            alpha[nb][j] = fast_exp2(acc.m[nb][j] - muse[nb][j]);
-            acc.m[nb][j] = mnew;
-        }
-    }
-    if (__any_sync(0xffffffffu, moved)) {
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-#pragma unroll
-            for (int mb = 0; mb < 8; ++mb) {
-                acc.o[nb][mb][0] *= alpha[nb][0]; acc.o[nb][mb][1] *= alpha[nb][1];
-                acc.o[nb][mb][2] *= alpha[nb][0]; acc.o[nb][mb][3] *= alpha[nb][1];
-            }
-            acc.l[nb][0] *= alpha[nb][0]; acc.z[nb][0] *= alpha[nb][0];
-            acc.l[nb][1] *= alpha[nb][1]; acc.z[nb][1] *= alpha[nb][1];
-        }
-    }
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-#pragma unroll
-        for (int grp = 0; grp < NG; ++grp) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                s[nb][grp][e] = fast_exp2(s[nb][grp][e] - muse[nb][e & 1]);
-                acc.l[nb][e & 1] += s[nb][grp][e];
-            }
-        }
-    }
-}
-
-// One sealed page (64 keys) of one KV head, staged in shared memory at `pg`: qk_page fills s with the masked
-// logits (log2 units), softmax_block turns them into p, pv_page accumulates p V.  (Computing the logits of the
-// next page between the softmax and the P V of this one was measured slower: more registers, no more overlap.)
-template <int NB, bool kOther>
-__device__ __forceinline__ void qk_page(const uint8_t* pg, const uint8_t* scratch, const QInt<NB>& qf, float (&s)[NB][4][4],
-                                        int lane, bool need_mask, int first_pos, const int (&row_lim)[NB][2], int key_begin,
-                                        int key_end) {
-    const int g = lane >> 2, t = lane & 3;
-    // ---- QK on the int8 tensor path: A = packed code bytes of keys (g, g+8) masked to their low / high nibbles,
-    //      B = 8-bit digits of (q' scale_K)^T; exact 32-bit accumulation
-#pragma unroll
-    for (int grp = 0; grp < 4; ++grp) {
-        const uint4 ka = *reinterpret_cast<const uint4*>(pg + kKCodeOff + (grp * 16 + g) * 64 + 16 * t);
-        const uint4 kb8 = *reinterpret_cast<const uint4*>(pg + kKCodeOff + (grp * 16 + 8 + g) * 64 + 16 * t);
-        const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb8.x, kb8.y, kb8.z, kb8.w};
-        int ceh[NB][4], cel[NB][4], coh[NB][4], col[NB][4];
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) ceh[nb][e] = cel[nb][e] = coh[nb][e] = col[nb][e] = 0;
-#pragma unroll
-        for (int kb = 0; kb < 2; ++kb) {
-            const uint32_t l0 = wa[2 * kb] & 0x0F0F0F0Fu, l1 = wb[2 * kb] & 0x0F0F0F0Fu, l2 = wa[2 * kb + 1] & 0x0F0F0F0Fu,
-                           l3 = wb[2 * kb + 1] & 0x0F0F0F0Fu;
-            const uint32_t h0 = wa[2 * kb] & 0xF0F0F0F0u, h1 = wb[2 * kb] & 0xF0F0F0F0u, h2 = wa[2 * kb + 1] & 0xF0F0F0F0u,
-                           h3 = wb[2 * kb + 1] & 0xF0F0F0F0u;
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-                imma16832(ceh[nb], l0, l1, l2, l3, qf.b[nb][kb][0][0][0], qf.b[nb][kb][0][0][1]);
-                imma16832(cel[nb], l0, l1, l2, l3, qf.b[nb][kb][0][1][0], qf.b[nb][kb][0][1][1]);
-                imma16832(coh[nb], h0, h1, h2, h3, qf.b[nb][kb][1][0][0], qf.b[nb][kb][1][0][1]);
-                imma16832(col[nb], h0, h1, h2, h3, qf.b[nb][kb][1][1][0], qf.b[nb][kb][1][1][1]);
-            }
-        }
-        float o0 = 1.0f, o1 = 1.0f;  // other_K of keys g and g+8 of the group
-        if constexpr (kOther) {
-            o0 = __half2float(*reinterpret_cast<const __half*>(scratch + 512 + (grp * 16 + g) * 2));
-            o1 = __half2float(*reinterpret_cast<const __half*>(scratch + 512 + (grp * 16 + 8 + g) * 2));
-        }
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                // 16 * sum = 256 (16 even_hi + odd_hi) + (16 even_lo + odd_lo); |.| < 2^31 for 64 code bytes per row
-                const int tot = ((ceh[nb][e] * 16 + coh[nb][e]) << 8) + (cel[nb][e] * 16 + col[nb][e]);
-                s[nb][grp][e] = fmaf(static_cast<float>(tot), qf.f[nb][e & 1], qf.qz[nb][e & 1]) * (e < 2 ? o0 : o1);
-            }
-        }
-    }
-    if (need_mask) {
-#pragma unroll
-        for (int grp = 0; grp < 4; ++grp) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int p = first_pos + grp * 16 + g + (e >> 1) * 8;
-                const bool out = p < key_begin || p >= key_end;
-#pragma unroll
-                for (int nb = 0; nb < NB; ++nb)
-                    if (out || p > row_lim[nb][e & 1]) s[nb][grp][e] = -INFINITY;
-            }
-        }
-    }
-}
-
+// Running maximum moves to mnew: rescale the accumulators of one row pair.  alpha = exp2(m_old - m_new).
 template <int NB>
-__device__ __forceinline__ void pv_page(const uint8_t* pg, const float (&s)[NB][4][4], Acc<NB>& acc, int lane) {
-    const int g = lane >> 2, t = lane & 3;
-    // ---- PV: A = V codes^T (dims x keys), B = (p scale_V)^T.  V scale page rows: [other other scale zp] per key
+__device__ __forceinline__ void rescale(Acc<NB>& acc, const float (&alpha)[NB][2]) {
 #pragma unroll
-    for (int grp = 0; grp < 4; ++grp) {
-        const float2 sz0 = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + kVScaleOff + (grp * 16 + g) * 8 + 4));
-        const float2 sz1 = unpack_half2(*reinterpret_cast<const uint32_t*>(pg + kVScaleOff + (grp * 16 + 8 + g) * 8 + 4));
-        uint32_t b0[NB], b1[NB];
+    for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-            const float(&p)[4] = s[nb][grp];
-            acc.z[nb][0] += p[0] * sz0.y + p[2] * sz1.y;
-            acc.z[nb][1] += p[1] * sz0.y + p[3] * sz1.y;
-            b0[nb] = movmatrix_trans(pack_half2(p[0] * sz0.x, p[1] * sz0.x));  // -> (row g; keys 2t, 2t+1)
-            b1[nb] = movmatrix_trans(pack_half2(p[2] * sz1.x, p[3] * sz1.x));  // -> (row g; keys 2t+8, 2t+9)
-        }
-        // lane (g, t): 16 dims 16g.. of keys 2t, 2t+1 (pa) and 2t+8, 2t+9 (pb), one half2 per dim
-        const uint8_t* vb = pg + kVCodeOff + (grp * 16 + 2 * t) * 64 + 8 * g;
-        const uint2 vA = *reinterpret_cast<const uint2*>(vb), vB = *reinterpret_cast<const uint2*>(vb + 64);
-        const uint2 vC = *reinterpret_cast<const uint2*>(vb + 512), vD = *reinterpret_cast<const uint2*>(vb + 576);
-        const uint32_t wa[2] = {vA.x, vA.y}, wb[2] = {vB.x, vB.y}, wc[2] = {vC.x, vC.y}, wd[2] = {vD.x, vD.y};
-        uint32_t pa[16], pb[16];
+        for (int db = 0; db < 4; ++db)
 #pragma unroll
-        for (int wi = 0; wi < 2; ++wi) {
+            for (int xy = 0; xy < 2; ++xy)
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const uint32_t sel = hh ? 0x7632u : 0x5410u;  // low / high 16 bits of both keys' words
-                const uint32_t x0 = prmt(wa[wi], wb[wi], sel), x1 = prmt(wc[wi], wd[wi], sel);
-                const uint32_t y0 = x0 >> 8, y1 = x1 >> 8;
-                const int d = 8 * wi + 4 * hh;
-                pa[d + 0] = hsub2_u32(lop3_and_or(x0, 0x000F000Fu, 0x64006400u), 0x64006400u);
-                pa[d + 1] = hsub2_u32(lop3_and_or(x0, 0x00F000F0u, 0x54005400u), 0x54005400u);
-                pa[d + 2] = hsub2_u32(lop3_and_or(y0, 0x000F000Fu, 0x64006400u), 0x64006400u);
-                pa[d + 3] = hsub2_u32(lop3_and_or(y0, 0x00F000F0u, 0x54005400u), 0x54005400u);
-                pb[d + 0] = hsub2_u32(lop3_and_or(x1, 0x000F000Fu, 0x64006400u), 0x64006400u);
-                pb[d + 1] = hsub2_u32(lop3_and_or(x1, 0x00F000F0u, 0x54005400u), 0x54005400u);
-                pb[d + 2] = hsub2_u32(lop3_and_or(y1, 0x000F000Fu, 0x64006400u), 0x64006400u);
-                pb[d + 3] = hsub2_u32(lop3_and_or(y1, 0x00F000F0u, 0x54005400u), 0x54005400u);
-            }
-        }
-#pragma unroll
-        for (int mb = 0; mb < 8; ++mb) {
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) mma16816(acc.o[nb][mb], pa[mb], pa[8 + mb], pb[mb], pb[8 + mb], b0[nb], b1[nb]);
-        }
+                for (int c = 0; c < 4; ++c) acc.o[nb][db][xy][c] *= alpha[nb][c & 1];
+        acc.l[nb][0] *= alpha[nb][0]; acc.z[nb][0] *= alpha[nb][0];
+        acc.l[nb][1] *= alpha[nb][1]; acc.z[nb][1] *= alpha[nb][1];
     }
 }
 
@@ -375,22 +226,21 @@ __device__ __forceinline__ void process_stage_group(const __half* krow, const __
                                                     Acc<NB>& acc, int lane, int first_pos, int kv_total,
                                                     const int (&row_lim)[NB][2], int key_begin, int key_end) {
     const int g = lane >> 2, t = lane & 3;
-    float s[NB][1][4];
+    float s[NB][4];
     {
         const __half* ka = krow + g * D + 32 * t;
         const __half* kb = krow + (8 + g) * D + 32 * t;
-        float c[NB][4];
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) c[nb][0] = c[nb][1] = c[nb][2] = c[nb][3] = 0.0f;
+        for (int nb = 0; nb < NB; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint4 a = *reinterpret_cast<const uint4*>(ka + 8 * i), b = *reinterpret_cast<const uint4*>(kb + 8 * i);
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
-                mma16816(c[nb], a.x, b.x, a.y, b.y, qf.hi[nb][2 * i][0], qf.hi[nb][2 * i][1]);
-                mma16816(c[nb], a.z, b.z, a.w, b.w, qf.hi[nb][2 * i + 1][0], qf.hi[nb][2 * i + 1][1]);
-                mma16816(c[nb], a.x, b.x, a.y, b.y, qf.lo[nb][2 * i][0], qf.lo[nb][2 * i][1]);
-                mma16816(c[nb], a.z, b.z, a.w, b.w, qf.lo[nb][2 * i + 1][0], qf.lo[nb][2 * i + 1][1]);
+                mma16816(s[nb], a.x, b.x, a.y, b.y, qf.hi[nb][2 * i][0], qf.hi[nb][2 * i][1]);
+                mma16816(s[nb], a.z, b.z, a.w, b.w, qf.hi[nb][2 * i + 1][0], qf.hi[nb][2 * i + 1][1]);
+                mma16816(s[nb], a.x, b.x, a.y, b.y, qf.lo[nb][2 * i][0], qf.lo[nb][2 * i][1]);
+                mma16816(s[nb], a.z, b.z, a.w, b.w, qf.lo[nb][2 * i + 1][0], qf.lo[nb][2 * i + 1][1]);
             }
         }
 #pragma unroll
@@ -398,148 +248,193 @@ __device__ __forceinline__ void process_stage_group(const __half* krow, const __
             const int p = first_pos + g + (e >> 1) * 8;
             const bool out = p >= kv_total || p < key_begin || p >= key_end;
 #pragma unroll
-            for (int nb = 0; nb < NB; ++nb) s[nb][0][e] = (out || p > row_lim[nb][e & 1]) ? -INFINITY : c[nb][e];
+            for (int nb = 0; nb < NB; ++nb)
+                if (out || p > row_lim[nb][e & 1]) s[nb][e] = -INFINITY;
         }
     }
-    softmax_block<NB, 1>(s, acc);
+    // online softmax over these 16 keys
+    float alpha[NB][2], muse[NB][2];
+    bool moved = false;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float mx = fmaxf(s[nb][j], s[nb][2 + j]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float mnew = fmaxf(acc.m[nb][j], mx);
+            moved |= mnew > acc.m[nb][j];
+            muse[nb][j] = mnew == -INFINITY ? 0.0f : mnew;
+            alpha[nb][j] = fast_exp2(acc.m[nb][j] - muse[nb][j]);
+            acc.m[nb][j] = mnew;
+        }
+    }
+    if (__any_sync(0xffffffffu, moved)) rescale<NB>(acc, alpha);
     uint32_t b0[NB], b1[NB];
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
-        b0[nb] = movmatrix_trans(pack_half2(s[nb][0][0], s[nb][0][1]));
-        b1[nb] = movmatrix_trans(pack_half2(s[nb][0][2], s[nb][0][3]));
-    }
-    // keys at or beyond kv_total hold stale rows: their p is exactly 0; zero V there so 0 * inf cannot appear
-    const __half* vb = vrow + (2 * t) * D + 16 * g;
-    uint4 v[4][2];
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-        const int key = 2 * t + (kk & 1) + (kk >> 1) * 8;
-        const bool live = first_pos + key < kv_total;
-        const uint4* src = reinterpret_cast<const uint4*>(vb + ((kk & 1) + (kk >> 1) * 8) * D);
-        v[kk][0] = live ? src[0] : make_uint4(0, 0, 0, 0);
-        v[kk][1] = live ? src[1] : make_uint4(0, 0, 0, 0);
-    }
-    uint32_t pa[16], pb[16];
-#pragma unroll
-    for (int h8 = 0; h8 < 2; ++h8) {
-        const uint32_t wa[4] = {v[0][h8].x, v[0][h8].y, v[0][h8].z, v[0][h8].w};
-        const uint32_t wb[4] = {v[1][h8].x, v[1][h8].y, v[1][h8].z, v[1][h8].w};
-        const uint32_t wc[4] = {v[2][h8].x, v[2][h8].y, v[2][h8].z, v[2][h8].w};
-        const uint32_t wd[4] = {v[3][h8].x, v[3][h8].y, v[3][h8].z, v[3][h8].w};
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {  // register r holds dims 8 h8 + 2r, +1 of one key
-            pa[8 * h8 + 2 * r] = prmt(wa[r], wb[r], 0x5410); pa[8 * h8 + 2 * r + 1] = prmt(wa[r], wb[r], 0x7632);
-            pb[8 * h8 + 2 * r] = prmt(wc[r], wd[r], 0x5410); pb[8 * h8 + 2 * r + 1] = prmt(wc[r], wd[r], 0x7632);
+        for (int e = 0; e < 4; ++e) {
+            s[nb][e] = fast_exp2(s[nb][e] - muse[nb][e & 1]);
+            acc.l[nb][e & 1] += s[nb][e];
         }
+        b0[nb] = movmatrix_trans(pack_half2(s[nb][0], s[nb][1]));  // -> (row g; keys 2t, 2t+1)
+        b1[nb] = movmatrix_trans(pack_half2(s[nb][2], s[nb][3]));  // -> (row g; keys 2t+8, 2t+9)
     }
+    // A = V^T: the lane supplies dims 32 db + 4g .. +3 of keys 2t, 2t+1, 2t+8, 2t+9.  Keys at or beyond kv_total hold
+    // stale rows: their p is exactly 0; zero V there so 0 * inf cannot appear.
 #pragma unroll
-    for (int mb = 0; mb < 8; ++mb) {
+    for (int db = 0; db < 4; ++db) {
+        uint2 v[4];
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) mma16816(acc.o[nb][mb], pa[mb], pa[8 + mb], pb[mb], pb[8 + mb], b0[nb], b1[nb]);
+        for (int kk = 0; kk < 4; ++kk) {
+            const int key = 2 * t + (kk & 1) + (kk >> 1) * 8;
+            const bool live = first_pos + key < kv_total;
+            v[kk] = live ? *reinterpret_cast<const uint2*>(vrow + key * D + 32 * db + 4 * g) : make_uint2(0u, 0u);
+        }
+        const uint32_t x0 = prmt(v[0].x, v[1].x, 0x5410), x1 = prmt(v[0].y, v[1].y, 0x5410);  // dims 4g, 4g+2 of keys 2t, 2t+1
+        const uint32_t x2 = prmt(v[2].x, v[3].x, 0x5410), x3 = prmt(v[2].y, v[3].y, 0x5410);  // ... of keys 2t+8, 2t+9
+        const uint32_t y0 = prmt(v[0].x, v[1].x, 0x7632), y1 = prmt(v[0].y, v[1].y, 0x7632);  // dims 4g+1, 4g+3
+        const uint32_t y2 = prmt(v[2].x, v[3].x, 0x7632), y3 = prmt(v[2].y, v[3].y, 0x7632);
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            mma16816(acc.o[nb][db][0], x0, x1, x2, x3, b0[nb], b1[nb]);
+            mma16816(acc.o[nb][db][1], y0, y1, y2, y3, b0[nb], b1[nb]);
+        }
     }
 }
 
-// The work of one CTA: split `split` (P.nsplit = the open tile) of KV head `head`, row block `zb`; its partial goes
-// to rows pidx .. pidx + 15 of the workspace.
-template <int NB, bool kOther>
+// The work of one CTA: split `split` of KV head `head`, row block `zb`; its partial goes to rows pidx .. pidx + 15 of
+// the workspace.  NB = 8-row blocks of query rows; a pass = the keys whose logits are held at once (a whole tile for
+// NB = 1, one page for NB = 2).
+template <int NB, int W>
 __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int head, int zb, int64_t pidx) {
+    constexpr int kWarps = W, kThreads = W * 32;
+    constexpr int kPassKeys = NB == 1 ? 128 : 64;
+    constexpr int kPasses = kTile / kPassKeys;     // passes per tile
+    constexpr int kPassChunks = kPassKeys / kChunkKeys;  // K chunks (= V chunks) per pass
+    constexpr int kPassGroups = kPassKeys / 16;
+    constexpr int kDimSweeps = NB;                 // the V chunks of a pass are swept once per 128 / NB dims
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    AttnSmem& sm = *reinterpret_cast<AttnSmem*>(smem_raw);
+    AttnSmem<W>& sm = *reinterpret_cast<AttnSmem<W>*>(smem_raw);
     const LayerView& L = P.L;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = L.q_heads / L.kv_heads;
+    WarpRing& R = sm.ring[warp];
     // ---- order of the first memory requests: the few bytes everything waits for (positions, q rows, page table
-    //      entries) go out first, then the first page of every warp, then -- after the rotation of q, about a
-    //      microsecond later -- the second page.  At short contexts the whole cache is requested in this first burst:
-    //      requested in this order the small loads do not queue behind it and all first pages land before any second.
-    uint16_t qraw[NB][4];
-    int qpos[NB];
+    //      entries) go out first, then the first chunks of every warp, then -- after the rotation of q -- the rest of
+    //      the ring.
+    uint16_t qraw[2][4];
+    int qpos[2] = {-1, -1};
 #pragma unroll
-    for (int i = 0; i < NB; ++i) {  // warp w prepares rows w and w + 8 of the block
-        const int R = zb * kRows + warp + kWarps * i, tq = R / G, gq = R % G;
-        qpos[i] = -1;
+    for (int i = 0; i < 2; ++i) {  // warps 0..7 prepare rows w and w + 8 of the block
         qraw[i][0] = qraw[i][1] = qraw[i][2] = qraw[i][3] = 0;
-        if (tq < P.T) {
-            const uint16_t* qrow = P.q + (static_cast<int64_t>(tq) * L.q_heads + head * G + gq) * D;
+        if (i < NB && warp < 8) {
+            const int Rr = zb * kRows + warp + 8 * i, tq = Rr / G, gq = Rr % G;
+            if (tq < P.T) {
+                const uint16_t* qrow = P.q + (static_cast<int64_t>(tq) * L.q_heads + head * G + gq) * D;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) qraw[i][j] = qrow[lane + 32 * j];
-            qpos[i] = P.pos[tq];
+                for (int j = 0; j < 4; ++j) qraw[i][j] = qrow[lane + 32 * j];
+                qpos[i] = P.pos[tq];
+            }
         }
     }
     const int kv_total = *P.total_pos + 1;
     const int key_end = min(P.key_end, kv_total), key_begin = max(P.key_begin, 0);
-    const int sealed_pages = 2 * (kv_total / kTile);
+    const int sealed_tiles = kv_total / kTile;
 
-    uint64_t* bars = sm.bars[warp];
     if (lane == 0) {
-        mbar_init(&bars[0], 1);
-        mbar_init(&bars[1], 1);
+#pragma unroll
+        for (int s = 0; s < kSlots; ++s) mbar_init(&R.bars[s], 1);
+        mbar_init(&R.hbars[0], 1);
+        mbar_init(&R.hbars[1], 1);
         mbar_fence_init();
     }
+    __syncwarp();
     const int32_t* tbl = L.table();
-    auto issue = [&](int32_t page, int slot) {  // lane 0: four bulk copies of one page into a slot
-        uint8_t* dst = sm.slots[warp][slot];
-        mbar_expect_tx(&bars[slot], kPageBytes);
-        bulk_g2s(dst + kKCodeOff, L.k_code + page_head_offset(64, L.kv_heads, page, head), 4096, &bars[slot]);
-        bulk_g2s(dst + kVCodeOff, L.v_code + page_head_offset(64, L.kv_heads, page, head), 4096, &bars[slot]);
-        bulk_g2s(dst + kKScaleOff, L.k_scale + page_head_offset(5, L.kv_heads, page, head), 640, &bars[slot]);
-        bulk_g2s(dst + kVScaleOff, L.v_scale + page_head_offset(4, L.kv_heads, page, head), 512, &bars[slot]);
-    };
+    // tiles of this CTA, then of this warp
+    int w0, w1;
+    {
+        const int tb = min(key_begin / kTile, sealed_tiles), te = min((key_end + kTile - 1) / kTile, sealed_tiles);
+        const int n = max(te - tb, 0);
+        const int c0 = tb + static_cast<int>(static_cast<int64_t>(n) * split / P.nsplit);
+        const int c1 = tb + static_cast<int>(static_cast<int64_t>(n) * (split + 1) / P.nsplit);
+        w0 = c0 + (c1 - c0) * warp / kWarps;
+        w1 = c0 + (c1 - c0) * (warp + 1) / kWarps;
+    }
+    const int ntiles = w1 - w0, nchunks = 8 * ntiles;
     // Page table entries are read 32 at a time, one per lane, a full batch ahead of their use: lane l of `ids`
     // knows the physical page of logical page ids_base + l, `ids_next` the 32 after those.
-    int w0 = 0, w1 = 0, ids_base = 0;
-    int32_t ids = -1, ids_next = -1;
-    auto load_ids = [&](int base) -> int32_t { return base + lane < w1 ? L.page_of(tbl, base + lane) : -1; };
+    int ids_base = 2 * w0;
+    auto load_ids = [&](int base) -> int32_t { return base + lane < 2 * w1 ? L.page_of(tbl, base + lane) : -1; };
+    int32_t ids = ntiles > 0 ? load_ids(ids_base) : -1, ids_next = ntiles > 0 ? load_ids(ids_base + 32) : -1;
     auto page_id = [&](int lp) -> int32_t {  // whole warp; lp in [ids_base, ids_base + 64)
         const int k = lp - ids_base;
         const int32_t a = __shfl_sync(0xffffffffu, ids, k & 31), b = __shfl_sync(0xffffffffu, ids_next, k & 31);
         return k < 32 ? a : b;
     };
-    uint32_t ok_mask = 0;  // bit s: slot s holds a page in flight / ready
-    int32_t second_page = -1;
-    if (split < P.nsplit) {  // sealed pages of this CTA, then of this warp
-        const int pb = min(key_begin / kPage, sealed_pages), pe = min((key_end + kPage - 1) / kPage, sealed_pages);
-        const int n = max(pe - pb, 0);
-        const int c0 = pb + static_cast<int>(static_cast<int64_t>(n) * split / P.nsplit);
-        const int c1 = pb + static_cast<int>(static_cast<int64_t>(n) * (split + 1) / P.nsplit);
-        // A warp that starts in the middle of a tile pays the per-tile set-up (scale transpose, q digits) for two
-        // tiles where one would do: around one or two tiles per warp, warps take whole tiles (measured: 6 % faster at
-        // 32,768 tokens; with longer ranges the extra set-up no longer shows and page granularity balances better).
-        const int u0 = c0 >> 1, u1 = (c1 + 1) >> 1;  // tiles the CTA touches
-        if (u1 - u0 >= kWarps - 1 && u1 - u0 <= 2 * kWarps) {
-            w0 = max(c0, 2 * (u0 + (u1 - u0) * warp / kWarps));
-            w1 = min(c1, 2 * (u0 + (u1 - u0) * (warp + 1) / kWarps));
-            if (w1 < w0) w1 = w0;
-        } else {
-            w0 = c0 + (c1 - c0) * warp / kWarps;
-            w1 = c0 + (c1 - c0) * (warp + 1) / kWarps;
+    // chunk n of this warp: tile w0 + n / 8; within the tile the chunks come in consumption order
+    auto chunk_src = [&](int n, int& lp, int& is_v, int& half) {
+        const int j = n & 7;
+        int page;
+        if constexpr (kPasses == 1) { is_v = j >> 2; page = (j >> 1) & 1; }
+        else { page = j >> 2; is_v = (j >> 1) & 1; }
+        half = j & 1;
+        lp = 2 * (w0 + (n >> 3)) + page;
+    };
+    uint32_t bad_chunks = 0;  // bit s: the chunk now assigned to slot s has no valid page (bad table entry): skip it
+    auto issue_chunk = [&](int n, int slot) {  // whole warp (page id by shuffle); lane 0 issues
+        int lp, is_v, half;
+        chunk_src(n, lp, is_v, half);
+        const int32_t page = page_id(lp);
+        if (page < 0) { bad_chunks |= 1u << slot; return; }
+        bad_chunks &= ~(1u << slot);
+        if (lane == 0) {
+            const uint8_t* src = (is_v ? L.v_code : L.k_code) + page_head_offset(64, L.kv_heads, page, head) + half * kChunkBytes;
+            mbar_expect_tx(&R.bars[slot], kChunkBytes);
+            bulk_g2s(R.slots[slot], src, kChunkBytes, &R.bars[slot]);
         }
-        ids_base = w0;
-        ids = load_ids(w0);
-        ids_next = load_ids(w0 + 32);
-        const int32_t p0 = __shfl_sync(0xffffffffu, ids, 0), p1 = __shfl_sync(0xffffffffu, ids, 1);  // -1 beyond w1 or bad
-        ok_mask = (p0 >= 0 ? 1u : 0u) | (p1 >= 0 ? 2u : 0u);
-        second_page = p1;
-        if (lane == 0 && p0 >= 0) issue(p0, 0);
+    };
+    uint32_t bad_hdr = 0;
+    auto issue_header = [&](int ti) {  // whole warp
+        const int32_t p0 = page_id(2 * (w0 + ti)), p1 = page_id(2 * (w0 + ti) + 1);
+        const int hb = ti & 1;
+        if (p0 < 0 || p1 < 0) { bad_hdr |= 1u << hb; return; }
+        bad_hdr &= ~(1u << hb);
+        if (lane == 0) {
+            uint8_t* dst = R.hdr[hb];
+            mbar_expect_tx(&R.hbars[hb], kHdrBytes);
+            bulk_g2s(dst, L.k_scale + page_head_offset(5, L.kv_heads, p0, head), kHdrK, &R.hbars[hb]);
+            bulk_g2s(dst + kHdrK, L.v_scale + page_head_offset(4, L.kv_heads, p0, head), kHdrV, &R.hbars[hb]);
+            bulk_g2s(dst + kHdrK + kHdrV, L.v_scale + page_head_offset(4, L.kv_heads, p1, head), kHdrV, &R.hbars[hb]);
+        }
+    };
+    int n_issued = 0;
+    if (ntiles > 0) {
+        issue_header(0);
+        for (; n_issued < 2 && n_issued < nchunks; ++n_issued) issue_chunk(n_issued, n_issued);
     }
 
     // ---- q' = H q * scale * log2(e) for the rows of this block, stored in fragment order
 #pragma unroll
     for (int i = 0; i < NB; ++i) {
-        const int r = warp + kWarps * i;
-        float v[4];
+        if (warp < 8) {
+            const int r = warp + 8 * i;
+            float v[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[j] = L.dtype == KVB_DTYPE_BF16 ? in_to_f32<true>(qraw[i][j]) : in_to_f32<false>(qraw[i][j]);
-        hadamard_warp<D>(v, lane);  // rows beyond T are zeros and stay zeros
-        if (lane == 0) sm.row_pos[r] = qpos[i];
-        float* dst = reinterpret_cast<float*>(sm.qfrag);
+            for (int j = 0; j < 4; ++j) v[j] = L.dtype == KVB_DTYPE_BF16 ? in_to_f32<true>(qraw[i][j]) : in_to_f32<false>(qraw[i][j]);
+            hadamard_warp<D>(v, lane);  // rows beyond T are zeros and stay zeros
+            if (lane == 0) sm.row_pos[r] = qpos[i];
+            float* dst = reinterpret_cast<float*>(sm.qfrag);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int d = lane + 32 * j;  // -> lane' = (r%8)*4 + d/32, slot j' = (d%32)/4, component d%4
-            dst[(((r >> 3) * 8 + ((d & 31) >> 2)) * 32 + (r & 7) * 4 + (d >> 5)) * 4 + (d & 3)] = v[j] * P.scale_log2;
+            for (int j = 0; j < 4; ++j) {
+                const int d = lane + 32 * j;  // -> lane' = (r%8)*4 + d/32, slot j' = (d%32)/4, component d%4
+                dst[(((r >> 3) * 8 + ((d & 31) >> 2)) * 32 + (r & 7) * 4 + (d >> 5)) * 4 + (d & 3)] = v[j] * P.scale_log2;
+            }
         }
     }
-    if (lane == 0 && second_page >= 0) issue(second_page, 1);
+    for (; n_issued < kSlots && n_issued < nchunks; ++n_issued) issue_chunk(n_issued, n_issued);
     launch_dependents();  // the reduce kernel may take its place on the SMs; it waits for this grid's completion
     __syncthreads();
 
@@ -558,79 +453,300 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
-        for (int mb = 0; mb < 8; ++mb) acc.o[nb][mb][0] = acc.o[nb][mb][1] = acc.o[nb][mb][2] = acc.o[nb][mb][3] = 0.0f;
+        for (int db = 0; db < 4; ++db)
+#pragma unroll
+            for (int xy = 0; xy < 2; ++xy)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc.o[nb][db][xy][c] = 0.0f;
         acc.m[nb][0] = acc.m[nb][1] = -INFINITY;
         acc.l[nb][0] = acc.l[nb][1] = acc.z[nb][0] = acc.z[nb][1] = 0.0f;
     }
-    QFrag<NB> qf;   // fp16 fragments for the open tile (stage rows)
-    QInt<NB> qi;    // 8-bit digits for the quantised pages
-    bool timed_out = false;
 
-    if (split < P.nsplit) {
-        uint8_t* scratch = sm.scratch[warp];
-        uint32_t phase[2] = {0, 0};
-        int cur_tile = -1;
-        for (int lp = w0; lp < w1; ++lp) {
-            const int slot = (lp - w0) & 1;
-            if (lp - ids_base >= 32) {
-                ids = ids_next;
-                ids_base += 32;
-                ids_next = load_ids(ids_base + 32);
-            }
-            const bool valid = (ok_mask >> slot) & 1u;
-            if (valid) {
-                if (!mbar_wait_bounded(&bars[slot], phase[slot])) { timed_out = true; break; }
-                phase[slot] ^= 1u;
-                const uint8_t* pg = sm.slots[warp][slot];
-                if ((lp >> 1) != cur_tile) {  // per-dim scale / zero point are per tile (stored in both pages)
-                    cur_tile = lp >> 1;
-                    __syncwarp();
-                    transpose_k_scale(pg + kKScaleOff, scratch, lane);
-                    __syncwarp();
-                    build_qint<NB>(sm, scratch, lane, qi);
-                } else if constexpr (kOther) {
-                    __syncwarp();
-                    transpose_k_scale(pg + kKScaleOff, scratch, lane);
-                    __syncwarp();
-                }
-                const int first = lp * kPage;
-                const bool need_mask = first + kPage - 1 > min_lim || first < key_begin || first + kPage > key_end;
-                float s[NB][4][4];
-                qk_page<NB, kOther>(pg, scratch, qi, s, lane, need_mask, first, row_lim, key_begin, key_end);
-                softmax_block<NB, 4>(s, acc);
-                pv_page<NB>(pg, s, acc, lane);
-            }
-            // refill this slot with the page after next; the generic-proxy reads above must be ordered first
-            __syncwarp();
-            const int32_t np = lp + 2 < w1 ? page_id(lp + 2) : -1;
-            const uint32_t nv = np >= 0 ? 1u : 0u;
-            if (lane == 0 && nv) {
-                fence_proxy_async();
-                issue(np, slot);
-            }
-            ok_mask = (ok_mask & ~(1u << slot)) | (nv << slot);
-        }
-        if (timed_out) {
-            if (lane == 0) L.flag(KVB_ERR_WAIT_TIMEOUT);
-            // copies already issued must land before the CTA's shared memory is released: bounded second wait
-            for (int s2 = 0; s2 < kSlots; ++s2)
-                if ((ok_mask >> s2) & 1u) mbar_wait_bounded(&bars[s2], phase[s2]);
-        }
-    } else {
-        // ---- open tile: warp w takes keys 16w .. 16w+15 of the tile, un-quantised, from the stage
+    // ---- open tile (last split of the head): warp w < 8 takes keys 16w .. 16w+15 of the tile, un-quantised, from
+    //      the stage; its loads are in flight together with the first chunks of the ring
+    if (split == P.nsplit - 1 && warp < 8) {
         const int tile = kv_total / kTile, base = tile * kTile;
         const int first = base + 16 * warp;
         if (first < key_end && first + 16 > key_begin && first < kv_total) {
-            build_qfrag<false, NB>(sm, nullptr, lane, qf);
+            QFrag<NB> qf;
+            build_qfrag<NB>(sm, lane, qf);
             process_stage_group<NB>(L.stage_row(0, tile & 1, head, 16 * warp), L.stage_row(1, tile & 1, head, 16 * warp), qf,
                                     acc, lane, first, kv_total, row_lim, key_begin, key_end);
         }
     }
 
-    // ---- merge the 8 warps of the CTA (log-sum-exp) and store one partial per row
+    // ---- sealed tiles
+    bool timed_out = false;
+    int n_done = 0;            // chunks consumed
+    int slot = 0;              // slot of chunk n_done
+    uint32_t phases = 0;       // bit s: parity the next wait on slot s expects; bits 8, 9: the header barriers
+    auto wait_chunk = [&]() -> const uint8_t* {
+        if (!((bad_chunks >> slot) & 1u) && !timed_out && !mbar_wait_bounded(&R.bars[slot], (phases >> slot) & 1u)) timed_out = true;
+        return R.slots[slot];
+    };
+    auto release_chunk = [&]() {  // the chunk in `slot` has been read by every lane: refill the slot, advance
+        const bool was_bad = (bad_chunks >> slot) & 1u;
+        if (!was_bad) phases ^= 1u << slot;
+        __syncwarp();
+        if (n_issued < nchunks && !timed_out) {
+            if (lane == 0) fence_proxy_async();  // generic-proxy reads of the slot are ordered before the refill
+            issue_chunk(n_issued, slot);
+            ++n_issued;
+        } else {
+            bad_chunks |= 1u << slot;  // nothing in flight here any more
+        }
+        ++n_done;
+        slot = slot + 1 == kSlots ? 0 : slot + 1;
+    };
+
+    for (int ti = 0; ti < ntiles; ++ti) {
+        const int hb = ti & 1;
+        {   // page ids: keep the window [ids_base, ids_base + 64) ahead of every lookup of this tile and its prefetches
+            if (2 * (w0 + ti) - ids_base >= 32) {
+                ids = ids_next;
+                ids_base += 32;
+                ids_next = load_ids(ids_base + 32);
+            }
+        }
+        if (ti + 1 < ntiles && !timed_out) {  // the other header buffer was last read during tile ti - 1
+            __syncwarp();
+            if (lane == 0) fence_proxy_async();
+            issue_header(ti + 1);
+        }
+        const bool hdr_ok = !((bad_hdr >> hb) & 1u);
+        if (hdr_ok && !timed_out && !mbar_wait_bounded(&R.hbars[hb], (phases >> (8 + hb)) & 1u)) timed_out = true;
+        if (hdr_ok) phases ^= 1u << (8 + hb);
+        const uint8_t* hdr = R.hdr[hb];
+        QInt<NB> qi;
+        __syncwarp();
+        transpose_k_scale(hdr, R.scratch, lane);
+        __syncwarp();
+        build_qint<NB>(sm, R.scratch, lane, qi);
+
+#pragma unroll
+        for (int pass = 0; pass < kPasses; ++pass) {
+            const int first = (w0 + ti) * kTile + pass * kPassKeys;
+            const bool need_mask = first + kPassKeys - 1 > min_lim || first < key_begin || first + kPassKeys > key_end;
+            // ---- QK: integer logits of the pass
+            int tot[NB][kPassGroups][4];
+            uint64_t dead = 0;  // bit 4 grp + e (+ 32 nb): a key this row may not see (mask, range, or a page that could not be read)
+            bool any_dead = need_mask;
+#pragma unroll
+            for (int c = 0; c < kPassChunks; ++c) {
+                const bool skip = (bad_chunks >> slot) & 1u;
+                const uint8_t* ch = wait_chunk();
+#pragma unroll
+                for (int gc = 0; gc < 2; ++gc) {
+                    const int grp = 2 * c + gc;
+                    const uint4 ka = *reinterpret_cast<const uint4*>(ch + (gc * 16 + g) * 64 + 16 * t);
+                    const uint4 kb8 = *reinterpret_cast<const uint4*>(ch + (gc * 16 + 8 + g) * 64 + 16 * t);
+                    const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb8.x, kb8.y, kb8.z, kb8.w};
+                    int ceh[NB][4], cel[NB][4], coh[NB][4], col[NB][4];
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) ceh[nb][e] = cel[nb][e] = coh[nb][e] = col[nb][e] = 0;
+#pragma unroll
+                    for (int kb = 0; kb < 2; ++kb) {
+                        const uint32_t l0 = wa[2 * kb] & 0x0F0F0F0Fu, l1 = wb[2 * kb] & 0x0F0F0F0Fu, l2 = wa[2 * kb + 1] & 0x0F0F0F0Fu,
+                                       l3 = wb[2 * kb + 1] & 0x0F0F0F0Fu;
+                        const uint32_t h0 = wa[2 * kb] & 0xF0F0F0F0u, h1 = wb[2 * kb] & 0xF0F0F0F0u, h2 = wa[2 * kb + 1] & 0xF0F0F0F0u,
+                                       h3 = wb[2 * kb + 1] & 0xF0F0F0F0u;
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) {
+                            imma_us(ceh[nb], l0, l1, l2, l3, qi.b[nb][kb][0][0][0], qi.b[nb][kb][0][0][1]);
+                            imma_uu(cel[nb], l0, l1, l2, l3, qi.b[nb][kb][0][1][0], qi.b[nb][kb][0][1][1]);
+                            imma_us(coh[nb], h0, h1, h2, h3, qi.b[nb][kb][1][0][0], qi.b[nb][kb][1][0][1]);
+                            imma_uu(col[nb], h0, h1, h2, h3, qi.b[nb][kb][1][1][0], qi.b[nb][kb][1][1][1]);
+                        }
+                    }
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)  // 16 * sum = 256 (16 even_hi + odd_hi) + (16 even_lo + odd_lo); |.| < 2^31
+                            tot[nb][grp][e] = ((ceh[nb][e] * 16 + coh[nb][e]) << 8) + (cel[nb][e] * 16 + col[nb][e]);
+                    if (skip) {
+                        any_dead = true;
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) dead |= 0xFull << (32 * nb + 4 * grp);
+                    }
+                }
+                release_chunk();
+            }
+            if (any_dead) {
+#pragma unroll
+                for (int grp = 0; grp < kPassGroups; ++grp)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int p = first + grp * 16 + g + (e >> 1) * 8;
+                        const bool out = p < key_begin || p >= key_end;
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) {
+                            if (out || p > row_lim[nb][e & 1]) dead |= 1ull << (32 * nb + 4 * grp + e);
+                            if ((dead >> (32 * nb + 4 * grp + e)) & 1ull) tot[nb][grp][e] = INT_MIN;
+                        }
+                    }
+            }
+            // ---- softmax of the pass relative to its own row maxima; weights of the pass against the running state
+            float wq[NB][2];     // weight of the integer sums of this pass in the running accumulators
+            float pf[NB][kPassGroups][4];
+            {
+                // per-key scale of V: the largest of the pass bounds p * scale_V; one factor for all rows
+                const uint8_t* vsc = hdr + kHdrK + (kPasses == 1 ? 0 : pass * kHdrV);
+                float svmax = 0.0f;
+#pragma unroll
+                for (int i = 0; i < kPassKeys / 32; ++i)
+                    svmax = fmaxf(svmax, fabsf(__half2float(*reinterpret_cast<const __half*>(vsc + (lane + 32 * i) * 8 + 4))));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) svmax = fmaxf(svmax, __shfl_xor_sync(0xffffffffu, svmax, o));
+                const float F = svmax > 0.0f ? kPMax / svmax : 0.0f, invF = svmax * (1.0f / kPMax);
+                float alpha[NB][2], wpass[NB][2], cst[NB][2];
+                bool moved = false;
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        int mx = INT_MIN;
+#pragma unroll
+                        for (int grp = 0; grp < kPassGroups; ++grp) mx = max(mx, max(tot[nb][grp][j], tot[nb][grp][2 + j]));
+                        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                        const float mpass = mx == INT_MIN ? -INFINITY : fmaf(static_cast<float>(mx), qi.f[nb][j], qi.qz[nb][j]);
+                        const float mnew = fmaxf(acc.m[nb][j], mpass);
+                        moved |= mnew > acc.m[nb][j];
+                        const float muse = mnew == -INFINITY ? 0.0f : mnew;
+                        alpha[nb][j] = fast_exp2(acc.m[nb][j] - muse);
+                        wpass[nb][j] = fast_exp2(mpass - muse);
+                        cst[nb][j] = qi.qz[nb][j] - (mpass == -INFINITY ? 0.0f : mpass);
+                        acc.m[nb][j] = mnew;
+                        wq[nb][j] = wpass[nb][j] * invF;
+                    }
+                }
+                if (__any_sync(0xffffffffu, moved)) rescale<NB>(acc, alpha);
+                float lp[NB][2], zp[NB][2];
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) lp[nb][0] = lp[nb][1] = zp[nb][0] = zp[nb][1] = 0.0f;
+#pragma unroll
+                for (int grp = 0; grp < kPassGroups; ++grp) {
+                    // V scale rows are [other other scale zp] per key; the pages of the pass are contiguous in the header
+                    const float2 sz0 = unpack_half2(*reinterpret_cast<const uint32_t*>(vsc + (grp * 16 + g) * 8 + 4));      // (scale, zp) of key g
+                    const float2 sz1 = unpack_half2(*reinterpret_cast<const uint32_t*>(vsc + (grp * 16 + 8 + g) * 8 + 4));  // ... of key g + 8
+                    const float sf0 = sz0.x * F, sf1 = sz1.x * F;
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        float p[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            p[e] = fast_exp2(fmaf(static_cast<float>(tot[nb][grp][e]), qi.f[nb][e & 1], cst[nb][e & 1]));
+                            if (any_dead && ((dead >> (32 * nb + 4 * grp + e)) & 1ull)) p[e] = 0.0f;
+                            lp[nb][e & 1] += p[e];
+                        }
+                        zp[nb][0] += p[0] * sz0.y + p[2] * sz1.y;
+                        zp[nb][1] += p[1] * sz0.y + p[3] * sz1.y;
+                        pf[nb][grp][0] = fmaf(p[0], sf0, kMagic); pf[nb][grp][1] = fmaf(p[1], sf0, kMagic);
+                        pf[nb][grp][2] = fmaf(p[2], sf1, kMagic); pf[nb][grp][3] = fmaf(p[3], sf1, kMagic);
+                    }
+                }
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        acc.l[nb][j] = fmaf(lp[nb][j], wpass[nb][j], acc.l[nb][j]);
+                        acc.z[nb][j] = fmaf(zp[nb][j], wpass[nb][j], acc.z[nb][j]);
+                    }
+            }
+            // ---- 16-bit weights -> B fragments: accumulator layout (key g; rows 2t, 2t+1) -> operand layout (row g; keys)
+            uint32_t bh[NB][kPassGroups], bl[NB][kPassGroups];
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int grp = 0; grp < kPassGroups; ++grp) {
+                    const uint32_t y0 = movmatrix_trans(prmt(__float_as_uint(pf[nb][grp][0]), __float_as_uint(pf[nb][grp][1]), 0x5410));  // keys 2t, 2t+1
+                    const uint32_t y1 = movmatrix_trans(prmt(__float_as_uint(pf[nb][grp][2]), __float_as_uint(pf[nb][grp][3]), 0x5410));  // keys 2t+8, 2t+9
+                    bl[nb][grp] = prmt(y0, y1, 0x6420);
+                    bh[nb][grp] = prmt(y0, y1, 0x7531);
+                }
+            // ---- PV on the int8 path.  ldmatrix.trans hands lane (g, t) the code bytes of dims 32 db + 4g .. +3 for keys
+            //      2t, 2t+1 (+8, +16, +24) of the chunk; one byte permute gathers four keys of a dim pair, one AND isolates
+            //      the even dim (x) or 16 x the odd dim (y).
+            if constexpr (kDimSweeps > 1) {  // the V chunks of the pass stay in their slots for every sweep: wait for all first
+                int s2 = slot;
+#pragma unroll
+                for (int c = 0; c < kPassChunks; ++c) {
+                    if (!((bad_chunks >> s2) & 1u) && !timed_out && !mbar_wait_bounded(&R.bars[s2], (phases >> s2) & 1u)) timed_out = true;
+                    s2 = s2 + 1 == kSlots ? 0 : s2 + 1;
+                }
+            }
+#pragma unroll
+            for (int sweep = 0; sweep < kDimSweeps; ++sweep) {
+                constexpr int kDb = 4 / kDimSweeps;
+                int ix[NB][kDb][2][2][4];  // [nb][db][xy][digit][c]
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int d = 0; d < kDb; ++d)
+#pragma unroll
+                        for (int a = 0; a < 4; ++a)
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) ix[nb][d][a >> 1][a & 1][c] = 0;
+                int vslot = slot;  // sweeps before the last walk the slots without releasing them
+#pragma unroll
+                for (int c = 0; c < kPassChunks; ++c) {
+                    const bool last = sweep == kDimSweeps - 1;
+                    const int cs = last ? slot : vslot;
+                    const bool skip = (bad_chunks >> cs) & 1u;
+                    const uint8_t* ch = (kDimSweeps == 1) ? wait_chunk() : R.slots[cs];
+#pragma unroll
+                    for (int d = 0; d < kDb; ++d) {
+                        const int db = sweep * kDb + d;
+                        uint32_t r[4];
+                        ldsm_x4_trans(r, ch + lane * 64 + 16 * db);
+                        const uint32_t u0 = prmt(r[0], r[1], 0x6420), v0 = prmt(r[0], r[1], 0x7531);
+                        const uint32_t u1 = prmt(r[2], r[3], 0x6420), v1 = prmt(r[2], r[3], 0x7531);
+                        const uint32_t ax0 = u0 & 0x0F0F0F0Fu, ax1 = v0 & 0x0F0F0F0Fu, ax2 = u1 & 0x0F0F0F0Fu, ax3 = v1 & 0x0F0F0F0Fu;
+                        const uint32_t ay0 = u0 & 0xF0F0F0F0u, ay1 = v0 & 0xF0F0F0F0u, ay2 = u1 & 0xF0F0F0F0u, ay3 = v1 & 0xF0F0F0F0u;
+                        if (!skip) {
+#pragma unroll
+                            for (int nb = 0; nb < NB; ++nb) {
+                                imma_uu(ix[nb][d][0][0], ax0, ax1, ax2, ax3, bh[nb][2 * c], bh[nb][2 * c + 1]);
+                                imma_uu(ix[nb][d][0][1], ax0, ax1, ax2, ax3, bl[nb][2 * c], bl[nb][2 * c + 1]);
+                                imma_uu(ix[nb][d][1][0], ay0, ay1, ay2, ay3, bh[nb][2 * c], bh[nb][2 * c + 1]);
+                                imma_uu(ix[nb][d][1][1], ay0, ay1, ay2, ay3, bl[nb][2 * c], bl[nb][2 * c + 1]);
+                            }
+                        }
+                    }
+                    if (last) release_chunk();
+                    else vslot = vslot + 1 == kSlots ? 0 : vslot + 1;
+                }
+                // ---- integer sums of the pass -> running fp32 accumulators
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int d = 0; d < kDb; ++d)
+#pragma unroll
+                        for (int xy = 0; xy < 2; ++xy)
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const float v = static_cast<float>((ix[nb][d][xy][0][c] << 8) + ix[nb][d][xy][1][c]);
+                                acc.o[nb][sweep * kDb + d][xy][c] = fmaf(v, wq[nb][c & 1] * (xy ? 0.0625f : 1.0f), acc.o[nb][sweep * kDb + d][xy][c]);
+                            }
+            }
+        }
+    }
+    if (timed_out) {
+        if (lane == 0) L.flag(KVB_ERR_WAIT_TIMEOUT);
+        // copies already issued must land before the CTA's shared memory is released: one more bounded wait each
+        for (int s = 0; s < kSlots; ++s)
+            if (!((bad_chunks >> s) & 1u)) mbar_wait_bounded(&R.bars[s], (phases >> s) & 1u);
+        for (int h = 0; h < 2; ++h) mbar_wait_bounded(&R.hbars[h], (phases >> (8 + h)) & 1u);
+    }
+
+    // ---- merge the warps of the CTA (log-sum-exp) and store one partial per row
     __syncthreads();  // every slot has been consumed: the ring memory becomes the merge buffer
     constexpr int kORow = D + 4, kWarpFloats = 3 * kRows + kRows * kORow;
-    float* mbuf = reinterpret_cast<float*>(sm.slots) + warp * kWarpFloats;
+    static_assert(kWarps * kWarpFloats * 4 <= static_cast<int>(sizeof(WarpRing)) * kWarps, "merge buffer exceeds the rings");
+    float* mbuf = reinterpret_cast<float*>(sm.ring) + warp * kWarpFloats;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
@@ -647,16 +763,16 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
                 mbuf[2 * kRows + row] = acc.z[nb][j];
             }
         }
-        float* ob = mbuf + 3 * kRows + (8 * nb + 2 * t) * kORow + 16 * g;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {  // component e: row 2t + (e & 1), dims 16g + 8 (e >> 1) ..
-            float* dst = ob + (e & 1) * kORow + (e >> 1) * 8;
-            *reinterpret_cast<float4*>(dst) = make_float4(acc.o[nb][0][e], acc.o[nb][1][e], acc.o[nb][2][e], acc.o[nb][3][e]);
-            *reinterpret_cast<float4*>(dst + 4) = make_float4(acc.o[nb][4][e], acc.o[nb][5][e], acc.o[nb][6][e], acc.o[nb][7][e]);
-        }
+        for (int db = 0; db < 4; ++db)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {  // row 8 nb + 2t + j, dims 32 db + 4g .. +3
+                float* dst = mbuf + 3 * kRows + (8 * nb + 2 * t + j) * kORow + 32 * db + 4 * g;
+                *reinterpret_cast<float4*>(dst) = make_float4(acc.o[nb][db][0][j], acc.o[nb][db][1][j], acc.o[nb][db][0][2 + j], acc.o[nb][db][1][2 + j]);
+            }
     }
     __syncthreads();
-    const float* all = reinterpret_cast<const float*>(sm.slots);
+    const float* all = reinterpret_cast<const float*>(sm.ring);
     for (int e = threadIdx.x; e < 8 * NB * (D / 4); e += kThreads) {  // one thread: four dims of one row
         const int row = e / (D / 4), d = 4 * (e % (D / 4));
         float m = -INFINITY;
@@ -680,11 +796,11 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
     }
 }
 
-template <int NB, bool kOther>
-__global__ void __launch_bounds__(kThreads, 1) attn_kernel(const AttnParams P) {
+template <int NB, int W>
+__global__ void __launch_bounds__(W * 32, 1) attn_kernel(const AttnParams P) {
     grid_dependency_wait();  // q, the positions and the cache come from the kernels before this one
     const int head = blockIdx.y, zb = blockIdx.z, split = blockIdx.x;
-    attn_cta<NB, kOther>(P, split, head, zb, ((static_cast<int64_t>(head) * gridDim.z + zb) * (P.nsplit + 1) + split) * kRows);
+    attn_cta<NB, W>(P, split, head, zb, ((static_cast<int64_t>(head) * gridDim.z + zb) * P.nsplit + split) * kRows);
 }
 
 // Batched decode: `n` independent sequences (their caches described by device-resident kvb_layer structs, same
@@ -701,6 +817,7 @@ struct BatchParams {
     const uint16_t* q;        // [n][q_heads][D]
     const int32_t* pos;       // [n] position of the newest token of each sequence
     float scale_log2;
+    int kv_heads, q_heads, dtype;  // geometry of the call: every entry must agree with it
     float* ws_m;              // [H][total parts][16]
     float* ws_l;
     float* ws_o;
@@ -717,26 +834,35 @@ __device__ __forceinline__ int batch_entry_of(const BatchPlan& plan, int part) {
     return lo;
 }
 
-template <int NB>
-__global__ void __launch_bounds__(kThreads, 1) attn_batch_kernel(const BatchParams B) {
+template <int NB, int W>
+__global__ void __launch_bounds__(W * 32, 1) attn_batch_kernel(const BatchParams B) {
+    constexpr int kThreads = W * 32;
     grid_dependency_wait();
     const int part = blockIdx.x, head = blockIdx.y;
     const int b = batch_entry_of(B.plan, part);
     AttnParams P;
     P.L = B.layers[b];
-    if ((P.L.head_dim != D || P.L.iters != 0) && threadIdx.x == 0) P.L.flag(KVB_ERR_GEOMETRY);  // results undefined, no fault
-    P.q = B.q + static_cast<int64_t>(b) * P.L.q_heads * D;
+    const int64_t pidx = (static_cast<int64_t>(head) * gridDim.x + part) * kRows;
+    if (P.L.head_dim != D || P.L.iters != 0 || P.L.kv_heads != B.kv_heads || P.L.q_heads != B.q_heads || P.L.dtype != B.dtype) {
+        // an entry that disagrees with the call's geometry is flagged and contributes nothing: its partial reads as
+        // "no key seen", so the merge writes zeros for that sequence and no plane is indexed with foreign strides
+        if (threadIdx.x == 0) P.L.flag(KVB_ERR_GEOMETRY);
+        for (int e = threadIdx.x; e < kRows * D; e += kThreads) B.ws_o[pidx * D + e] = 0.0f;
+        if (threadIdx.x < kRows) { B.ws_m[pidx + threadIdx.x] = -INFINITY; B.ws_l[pidx + threadIdx.x] = 0.0f; }
+        return;
+    }
+    P.q = B.q + static_cast<int64_t>(b) * B.q_heads * D;
     P.pos = B.pos + b;
     P.total_pos = B.pos + b;
     P.T = 1;
     P.scale_log2 = B.scale_log2;
-    P.nsplit = B.plan.prefix[b + 1] - B.plan.prefix[b] - 1;
+    P.nsplit = B.plan.prefix[b + 1] - B.plan.prefix[b];
     P.key_begin = 0;
     P.key_end = INT_MAX;
     P.ws_m = B.ws_m;
     P.ws_l = B.ws_l;
     P.ws_o = B.ws_o;
-    attn_cta<NB, false>(P, part - B.plan.prefix[b], head, 0, (static_cast<int64_t>(head) * gridDim.x + part) * kRows);
+    attn_cta<NB, W>(P, part - B.plan.prefix[b], head, 0, pidx);
 }
 
 // Merge the partials of all splits of one query row, normalise, rotate back (H is its own inverse) and
@@ -761,15 +887,17 @@ struct PushTarget {
     uint32_t* error_word;
     int rank, world;                           // world 0: no push
 };
+// One 16-byte access = two 64-bit elements, each {value (low half), call number (high half)}: the element type of
+// the vector access is 64 bits, so value and call number of a word are one access in the memory model, not two.
 __device__ __forceinline__ void ring_store2(unsigned long long* p, float a, float b, uint32_t call) {
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(__float_as_uint(a)), "r"(call), "r"(__float_as_uint(b)),
-                 "r"(call)
-                 : "memory");
+    const unsigned long long wa = static_cast<unsigned long long>(__float_as_uint(a)) | (static_cast<unsigned long long>(call) << 32);
+    const unsigned long long wb = static_cast<unsigned long long>(__float_as_uint(b)) | (static_cast<unsigned long long>(call) << 32);
+    asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(p), "l"(wa), "l"(wb) : "memory");
 }
 __device__ __forceinline__ uint4 ring_load2(const unsigned long long* p) {
-    uint4 w;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(p) : "memory");
-    return w;
+    unsigned long long wa, wb;
+    asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(wa), "=l"(wb) : "l"(p) : "memory");
+    return make_uint4(static_cast<uint32_t>(wa), static_cast<uint32_t>(wa >> 32), static_cast<uint32_t>(wb), static_cast<uint32_t>(wb >> 32));
 }
 __device__ __forceinline__ bool ring_arrived(const uint4& w, uint32_t call) { return w.y == call && w.w == call; }
 
@@ -991,16 +1119,13 @@ int sm_count() { return device_sm_count(); }
 
 int zblocks_of(int q_heads, int kv_heads, int rows) { return (rows * (q_heads / kv_heads) + kRows - 1) / kRows; }
 
-// Splits over the sealed pages: one CTA per SM in total, the open-tile CTAs included, at least one
-// page per warp where the context is long enough.
+// Splits over the sealed tiles of a head: one CTA per SM in total, no more splits than tiles.
 int split_count(int kv_len_max, int kv_heads, int zblocks) {
-    const int pages = 2 * (kv_len_max / kTile);
+    const int tiles = kv_len_max / kTile;
     const int per = kv_heads * zblocks;
-    int n = (sm_count() - per) / per;
-    n = n < 1 ? 1 : n;
-    const int by_pages = (pages + 1) / 2;  // at least two pages per CTA
-    if (n > by_pages) n = by_pages;
-    if (n > kReduceWarps * kMaxPartsPerWarp - 1) n = kReduceWarps * kMaxPartsPerWarp - 1;  // reduce_kernel holds 64 parts
+    int n = sm_count() / per;
+    if (n > tiles) n = tiles;
+    if (n > kReduceWarps * kMaxPartsPerWarp) n = kReduceWarps * kMaxPartsPerWarp;  // reduce_kernel holds 64 parts
     return n < 1 ? 1 : n;
 }
 
@@ -1035,7 +1160,7 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
                                         part_m, part_l, part_o, stream);
     const int Z = zblocks_of(layer->q_heads, layer->kv_heads, T);
     const int nsplit = split_count(kv_len_max, layer->kv_heads, Z);
-    const int parts = nsplit + 1;
+    const int parts = nsplit;
     AttnParams P;
     P.L = make_view(*layer);
     P.q = static_cast<const uint16_t*>(q);
@@ -1051,14 +1176,15 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     P.ws_l = P.ws_m + rows;
     P.ws_o = P.ws_l + rows;
     const bool upper = T * (layer->q_heads / layer->kv_heads) > 8;
-    const int smem = static_cast<int>(sizeof(AttnSmem));
+    constexpr int smem1 = static_cast<int>(sizeof(AttnSmem<kWarpsDecode>)), smem2 = static_cast<int>(sizeof(AttnSmem<kWarpsWide>));
     static unsigned long long opted = 0;
     if (first_call_on_device(opted)) {
-        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<1, kWarpsDecode>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
+        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<2, kWarpsWide>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
     }
     const dim3 grid(parts, layer->kv_heads, Z);
-    KVB_CUDA_OK(launch_early(upper ? attn_kernel<2, false> : attn_kernel<1, false>, grid, dim3(kThreads), smem, stream, P));
+    if (upper) KVB_CUDA_OK(launch_early(attn_kernel<2, kWarpsWide>, grid, dim3(kWarpsWide * 32), smem2, stream, P));
+    else KVB_CUDA_OK(launch_early(attn_kernel<1, kWarpsDecode>, grid, dim3(kWarpsDecode * 32), smem1, stream, P));
     const int total_rows = T * layer->q_heads;
     KVB_CUDA_OK(launch_early(reduce_kernel, dim3(total_rows), dim3(kReduceWarps * 32), 0, stream, P.ws_m, P.ws_l, P.ws_o, parts, T,
                              layer->q_heads, layer->kv_heads, Z, layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o,
@@ -1075,20 +1201,30 @@ static constexpr int kDenseRows = 32;
 extern "C" int kvb_split_capacity(int kv_len_max, int kv_heads, int q_heads, int rows, int batch) {
     (void)batch;
     if (kv_heads < 1 || q_heads < kv_heads || rows < 1) return 0;
-    return kvb::split_count(kv_len_max, kv_heads, kvb::zblocks_of(q_heads, kv_heads, rows)) + 1;
+    return kvb::split_count(kv_len_max, kv_heads, kvb::zblocks_of(q_heads, kv_heads, rows));
 }
 
-extern "C" size_t kvb_workspace_bytes(int kv_len_max, int kv_heads, int q_heads, int head_dim, int rows, int batch) {
-    if (kv_heads < 1 || q_heads < kv_heads || rows < 1 || batch < 1) return 0;
-    const int Z = kvb::zblocks_of(q_heads, kv_heads, rows);
-    const size_t parts = kvb::split_count(kv_len_max, kv_heads, Z) + 1;
+// Bytes one call with `r` query tokens needs (the split count, hence the size, is not monotonic in r).
+static size_t workspace_bytes_for_rows(int kv_len_max, int kv_heads, int q_heads, int head_dim, int r) {
+    const int Z = kvb::zblocks_of(q_heads, kv_heads, r);
+    const size_t parts = kvb::split_count(kv_len_max, kv_heads, Z);
     size_t bytes = static_cast<size_t>(kv_heads) * Z * parts * kvb::kRows * (head_dim + 2) * sizeof(float);
-    const size_t general = kvb::general_workspace_bytes(kv_len_max, q_heads, head_dim, rows);
+    const size_t general = kvb::general_workspace_bytes(kv_len_max, q_heads, head_dim, r);
     if (general > bytes) bytes = general;
-    if (rows * (q_heads / kv_heads) >= kDenseRows) {  // verify steps this wide run on the chunk-attention kernel
-        const size_t dense = kvb_prefill_workspace_bytes(kv_len_max, kv_heads, q_heads, head_dim, rows);
+    if (r * (q_heads / kv_heads) >= kDenseRows) {  // verify steps this wide run on the chunk-attention kernel
+        const size_t dense = kvb_prefill_workspace_bytes(kv_len_max, kv_heads, q_heads, head_dim, r);
         if (dense > bytes) bytes = dense;
     }
+    return bytes;
+}
+
+// A workspace of this size serves every call with 1..rows query tokens: the maximum over the widths, since a narrower
+// step can be cut into more splits than a wider one.
+extern "C" size_t kvb_workspace_bytes(int kv_len_max, int kv_heads, int q_heads, int head_dim, int rows, int batch) {
+    if (kv_heads < 1 || q_heads < kv_heads || rows < 1 || batch < 1) return 0;
+    size_t bytes = 0;
+    for (int r = 1; r <= rows && r <= 8; ++r) bytes = std::max(bytes, workspace_bytes_for_rows(kv_len_max, kv_heads, q_heads, head_dim, r));
+    if (rows > 8) bytes = std::max(bytes, workspace_bytes_for_rows(kv_len_max, kv_heads, q_heads, head_dim, rows));
     return static_cast<size_t>(batch) * bytes;
 }
 
@@ -1185,20 +1321,20 @@ static_assert(sizeof(LayerView) == sizeof(kvb_layer) && offsetof(LayerView, erro
                   offsetof(LayerView, iters) == offsetof(kvb_layer, sinkhorn_iters),
               "the device reads kvb_layer structs as LayerView");
 
-// Parts (splits over sealed pages + the open tile) of every sequence from the host's bounds of their lengths:
-// about eight CTAs per SM in total, at least 16 pages per split, at most 63 splits per sequence.
+// Parts (splits over the sealed tiles; the last one also reads the open tile) of every sequence from the host's
+// bounds of their lengths: about eight CTAs per SM in total, at least 8 tiles per split, at most 64 splits per sequence.
 int plan_batch(const int32_t* kv_len_max, int batch, int kv_heads, BatchPlan& plan) {
-    int64_t total_pages = 0;
-    for (int b = 0; b < batch; ++b) total_pages += 2 * (kv_len_max[b] / kTile);
+    int64_t total_tiles = 0;
+    for (int b = 0; b < batch; ++b) total_tiles += kv_len_max[b] / kTile;
     const int64_t want = std::max<int64_t>(batch, static_cast<int64_t>(8) * sm_count() / kv_heads);
-    const int64_t chunk = std::max<int64_t>(16, (total_pages + want - 1) / want);
+    const int64_t chunk = std::max<int64_t>(8, (total_tiles + want - 1) / want);
     plan.n = batch;
     plan.prefix[0] = 0;
     for (int b = 0; b < batch; ++b) {
-        const int64_t pages = 2 * (kv_len_max[b] / kTile);
-        int nsplit = static_cast<int>((pages + chunk - 1) / chunk);
-        nsplit = std::min(std::max(nsplit, 1), kReduceWarps * kMaxPartsPerWarp - 1);
-        plan.prefix[b + 1] = plan.prefix[b] + nsplit + 1;
+        const int64_t tiles = kv_len_max[b] / kTile;
+        int nsplit = static_cast<int>((tiles + chunk - 1) / chunk);
+        nsplit = std::min(std::max(nsplit, 1), kReduceWarps * kMaxPartsPerWarp);
+        plan.prefix[b + 1] = plan.prefix[b] + nsplit;
     }
     return plan.prefix[batch];
 }
@@ -1236,18 +1372,21 @@ extern "C" int kvb_attn_decode_batch(const kvb_layer* layers_dev, int batch, int
     B.q = static_cast<const uint16_t*>(q);
     B.pos = pos_dev;
     B.scale_log2 = scale * 1.4426950408889634f;
+    B.kv_heads = kv_heads;
+    B.q_heads = q_heads;
+    B.dtype = dtype;
     B.ws_m = static_cast<float*>(workspace);
     B.ws_l = B.ws_m + rows;
     B.ws_o = B.ws_l + rows;
-    const int smem = static_cast<int>(sizeof(AttnSmem));
+    constexpr int smem1 = static_cast<int>(sizeof(AttnSmem<kWarpsDecode>)), smem2 = static_cast<int>(sizeof(AttnSmem<kWarpsWide>));
     static unsigned long long opted = 0;
     if (first_call_on_device(opted)) {
-        KVB_CUDA_OK(cudaFuncSetAttribute(attn_batch_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        KVB_CUDA_OK(cudaFuncSetAttribute(attn_batch_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        KVB_CUDA_OK(cudaFuncSetAttribute(attn_batch_kernel<1, kWarpsDecode>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
+        KVB_CUDA_OK(cudaFuncSetAttribute(attn_batch_kernel<2, kWarpsWide>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const bool upper = q_heads / kv_heads > 8;
-    KVB_CUDA_OK(launch_early(upper ? attn_batch_kernel<2> : attn_batch_kernel<1>, dim3(total, kv_heads, 1), dim3(kThreads), smem, st, B));
+    if (q_heads / kv_heads > 8) KVB_CUDA_OK(launch_early(attn_batch_kernel<2, kWarpsWide>, dim3(total, kv_heads, 1), dim3(kWarpsWide * 32), smem2, st, B));
+    else KVB_CUDA_OK(launch_early(attn_batch_kernel<1, kWarpsDecode>, dim3(total, kv_heads, 1), dim3(kWarpsDecode * 32), smem1, st, B));
     KVB_CUDA_OK(launch_early(reduce_kernel, dim3(batch * q_heads), dim3(kReduceWarps * 32), 0, st, B.ws_m, B.ws_l, B.ws_o, 0, batch, q_heads,
                              kv_heads, 1, dtype, static_cast<uint16_t*>(out), static_cast<float*>(nullptr), static_cast<float*>(nullptr),
                              static_cast<float*>(nullptr), PushTarget{}, B.plan));
@@ -1256,7 +1395,8 @@ extern "C" int kvb_attn_decode_batch(const kvb_layer* layers_dev, int batch, int
 
 namespace kvb {
 int launch_chunk_attention(const kvb_layer* layer, const void* q, const int32_t* positions_dev, int tokens, float scale,
-                           int kv_len_max, void* workspace, void* out, cudaStream_t s);  // kvb_prefill.cu
+                           int kv_len_max, void* workspace, void* out, cudaStream_t s, float* part_m, float* part_l,
+                           float* part_o, const int32_t* total_pos_dev);  // kvb_prefill.cu
 }
 
 extern "C" int kvb_attn_verify(const kvb_layer* layer, const void* q, const void* k, const void* v,
@@ -1267,10 +1407,51 @@ extern "C" int kvb_attn_verify(const kvb_layer* layer, const void* q, const void
     if (int st = kvb_append(layer, k, v, positions_dev, width, stream)) return st;
     if (width * (layer->q_heads / layer->kv_heads) >= kDenseRows && layer->head_dim == 128 && layer->sinkhorn_iters == 0) {
         if (q == nullptr || workspace == nullptr || out == nullptr) return kvb::fail(KVB_EINVAL, "kvb_attn_verify: null q / workspace / out");
-        return kvb::launch_chunk_attention(layer, q, positions_dev, width, scale, kv_len_max, workspace, out, static_cast<cudaStream_t>(stream));
+        return kvb::launch_chunk_attention(layer, q, positions_dev, width, scale, kv_len_max, workspace, out, static_cast<cudaStream_t>(stream),
+                                           nullptr, nullptr, nullptr, nullptr);
     }
     return kvb::launch_attention(layer, q, positions_dev, positions_dev + (width - 1), width, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr,
                                  nullptr, static_cast<cudaStream_t>(stream), "kvb_attn_verify");
+}
+
+// Causal attention of `tokens` already-appended (or foreign) query rows over THIS cache alone, exported as log-sum-exp
+// partials: the building block of verify steps and prefill chunks over a sequence whose tile ranges live on several
+// GPUs.  The rows' positions are in this cache's own coordinates; a cache that holds an earlier range of the sequence
+// passes its last position for every row (every key visible).
+extern "C" int kvb_attn_chunk_partial(const kvb_layer* layer, const void* q, const int32_t* positions_dev, int tokens, float scale,
+                                      int kv_len_max, void* workspace, float* part_m, float* part_l, float* part_o, void* stream) {
+    using namespace kvb;
+    if (int st = check_layer(layer, "kvb_attn_chunk_partial")) return st;
+    if (tokens < 1 || tokens > 65535) return fail(KVB_ERANGE, "kvb_attn_chunk_partial: %d tokens (1..65535)", tokens);
+    if (q == nullptr || positions_dev == nullptr || workspace == nullptr || part_m == nullptr || part_l == nullptr || part_o == nullptr)
+        return fail(KVB_EINVAL, "kvb_attn_chunk_partial: null argument");
+    if (layer->stage == nullptr) return fail(KVB_EINVAL, "kvb_attn_chunk_partial: layer has no stage buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (layer->head_dim != 128 || layer->sinkhorn_iters != 0)
+        return launch_general_attention(layer, q, positions_dev, positions_dev + (tokens - 1), tokens, scale, kv_len_max, 0, INT_MAX, workspace,
+                                        nullptr, part_m, part_l, part_o, st);
+    if (tokens <= 8 && tokens * (layer->q_heads / layer->kv_heads) < kDenseRows)
+        return launch_attention(layer, q, positions_dev, positions_dev + (tokens - 1), tokens, scale, kv_len_max, 0, INT_MAX, workspace, nullptr,
+                                part_m, part_l, part_o, st, "kvb_attn_chunk_partial");
+    return launch_chunk_attention(layer, q, positions_dev, tokens, scale, kv_len_max, workspace, nullptr, st, part_m, part_l, part_o, nullptr);
+}
+
+// Causal attention of 1..8 query rows whose K/V rows are already in the cache -- a verify step without its append, for
+// callers that append a wide step once and attend it in column blocks.
+extern "C" int kvb_attn_rows(const kvb_layer* layer, const void* q, const int32_t* positions_dev, int rows, const int32_t* total_pos_dev,
+                             float scale, int kv_len_max, void* workspace, void* out, void* stream) {
+    using namespace kvb;
+    if (rows < 1 || rows > 8) return fail(KVB_ERANGE, "kvb_attn_rows: %d rows (1..8)", rows);
+    if (int st = check_layer(layer, "kvb_attn_rows")) return st;
+    if (total_pos_dev == nullptr) return fail(KVB_EINVAL, "kvb_attn_rows: null total_pos_dev");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rows * (layer->q_heads / layer->kv_heads) >= kDenseRows && layer->head_dim == 128 && layer->sinkhorn_iters == 0) {
+        if (q == nullptr || positions_dev == nullptr || workspace == nullptr || out == nullptr)
+            return fail(KVB_EINVAL, "kvb_attn_rows: null q / positions / workspace / out");
+        return launch_chunk_attention(layer, q, positions_dev, rows, scale, kv_len_max, workspace, out, st, nullptr, nullptr, nullptr, total_pos_dev);
+    }
+    return launch_attention(layer, q, positions_dev, total_pos_dev, rows, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr, nullptr,
+                            st, "kvb_attn_rows");
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -345,12 +345,16 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     if (warp == 0) tc::tmem_dealloc(sm.tmem_base, kTmemCols);
 }
 
-// Merge the key ranges of one query row, normalise, undo the tile dim order, rotate back, store.
+// Merge the key ranges of one query row, normalise, undo the tile dim order, rotate back, store -- or, for a cache
+// that holds only a range of the sequence, export the merged partial instead (m in natural-log units, l, o in the
+// rotated domain and natural dim order, not normalised).
 // One CTA of 8 warps per row: warp w takes ranges w, w+8, ..; lane l owns dims l + 32 j.  The loop is pure load
 // latency, so it is unrolled to keep several ranges in flight; the warp sums meet in shared memory.
 __global__ void __launch_bounds__(256) prefill_merge_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
                                                             const float* __restrict__ ws_o, int T, int q_heads, int kv_heads,
-                                                            int mtiles, int ksplit, int dtype, uint16_t* __restrict__ out) {
+                                                            int mtiles, int ksplit, int dtype, uint16_t* __restrict__ out,
+                                                            float* __restrict__ part_m, float* __restrict__ part_l,
+                                                            float* __restrict__ part_o) {
     __shared__ float so[8][D];
     __shared__ float sl[8];
     const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -384,6 +388,12 @@ __global__ void __launch_bounds__(256) prefill_merge_kernel(const float* __restr
         l += sl[w];
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[j] += so[w][lane + 32 * j];
+    }
+    if (part_m != nullptr) {
+        if (lane == 0) { part_m[row] = m * 0.6931471805599453f; part_l[row] = l; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) part_o[static_cast<int64_t>(row) * D + lane + 32 * j] = o[j];
+        return;
     }
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
 #pragma unroll
@@ -432,12 +442,13 @@ extern "C" size_t kvb_prefill_workspace_bytes(int kv_len_max, int kv_heads, int 
 namespace kvb {
 // Chunk attention of `tokens` rows that are already appended (shared by the prefill and the verify entry points).
 int launch_chunk_attention(const kvb_layer* layer, const void* q, const int32_t* positions_dev, int tokens, float scale,
-                           int kv_len_max, void* workspace, void* out, cudaStream_t s) {
+                           int kv_len_max, void* workspace, void* out, cudaStream_t s, float* part_m, float* part_l,
+                           float* part_o, const int32_t* total_pos_dev) {
     PrefillParams P;
     P.L = make_view(*layer);
     P.q = static_cast<const uint16_t*>(q);
     P.pos = positions_dev;
-    P.total_pos = positions_dev + (tokens - 1);
+    P.total_pos = total_pos_dev != nullptr ? total_pos_dev : positions_dev + (tokens - 1);
     P.T = tokens;
     prefill_shape(kv_len_max, layer->kv_heads, layer->q_heads, tokens, &P.mtiles, &P.ksplit);
     P.scale_log2 = scale * 1.4426950408889634f;
@@ -454,7 +465,7 @@ int launch_chunk_attention(const kvb_layer* layer, const void* q, const int32_t*
     KVB_CUDA_OK(cudaGetLastError());
     const int total_rows = tokens * layer->q_heads;
     prefill_merge_kernel<<<total_rows, 256, 0, s>>>(P.ws_m, P.ws_l, P.ws_o, tokens, layer->q_heads, layer->kv_heads, P.mtiles,
-                                                    P.ksplit, layer->dtype, static_cast<uint16_t*>(out));
+                                                    P.ksplit, layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o);
     KVB_CUDA_OK(cudaGetLastError());
     return KVB_OK;
 }
@@ -473,5 +484,6 @@ extern "C" int kvb_attn_prefill(const kvb_layer* layer, const void* q, const voi
     if (layer->head_dim != 128 || layer->sinkhorn_iters != 0)  // shapes outside the tensor-core kernel: general kernel, same semantics
         return launch_general_attention(layer, q, positions_dev, positions_dev + (tokens - 1), tokens, scale, kv_len_max, 0, INT_MAX,
                                         workspace, out, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
-    return launch_chunk_attention(layer, q, positions_dev, tokens, scale, kv_len_max, workspace, out, static_cast<cudaStream_t>(stream));
+    return launch_chunk_attention(layer, q, positions_dev, tokens, scale, kv_len_max, workspace, out, static_cast<cudaStream_t>(stream),
+                                  nullptr, nullptr, nullptr, nullptr);
 }

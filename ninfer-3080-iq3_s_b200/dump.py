@@ -1,6 +1,7 @@
-"""KV dump files the reference's host verifier reads: KVD1 (quantised records taken from the planes) and KVO1
-(what the engine de-quantised from them), kvarn-evidence/verify-g128/README.md:45-135; the engine writes the same
-two files under KVARN128_DUMP_DIR (kvarn-port/patches/0004-*.patch, kvarn128_launch.cu:680-718).
+"""KV dump files of the reference: KVD1 (quantised records taken from the planes) and KVO1 (what the engine
+de-quantised from them), which its host verifier reads (kvarn-evidence/verify-g128/README.md:45-135; the engine writes
+the same two files under KVARN128_DUMP_DIR, kvarn-port/patches/0004-*.patch, kvarn128_launch.cu:680-718), and GVK2, the
+record dump its byte-for-byte quantiser gate compares (kvarn-evidence/gate2-kvarn-quant/dump_oracle.cpp:725-729).
 
 Host-side, numpy only: the planes are copied off the device by the caller.  A *record* is one 128 x 128 slice of
 one (tile, head, K | V): K has row = dim, col = token; V has row = token, col = dim.  Its code bytes are the
@@ -17,6 +18,7 @@ import numpy as np
 
 TILE, PAGE, SLICE = 128, 64, 128
 KVD1_MAGIC, KVO1_MAGIC = 0x3144564B, 0x314F564B  # 'KVD1', 'KVO1'
+GVK2_MAGIC = b"GVK2"
 
 
 @dataclass
@@ -178,3 +180,79 @@ def dequantise(record: Record) -> np.ndarray:
     z = record.zp_axis.view(np.float16).astype(np.float32)[:, None]
     o = record.other_axis.view(np.float16).astype(np.float32)[None, :]
     return ((q * s).astype(np.float32) + z).astype(np.float32) * o
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# GVK2: per record the quantiser's input tile (fp32, already fp16-exact), the balancing factors it settled on and
+# the full record bytes = code payload | scale_axis | zp_axis | other_axis (fp16), the layout of the reference
+# oracle's record (bee_oracle.cpp:309-314).
+@dataclass
+class Gvk2Entry:
+    name: str
+    bits: int
+    iters: int
+    best_iter: int
+    best_imbalance: float
+    s_col: np.ndarray   # float32 [cols]
+    s_row: np.ndarray   # float32 [rows]
+    tile: np.ndarray    # float32 [rows][cols]
+    record: np.ndarray  # uint8 [rows * cols * bits / 8 + 2 * (2 * rows + cols)]
+
+
+def record_bytes(record: Record) -> np.ndarray:
+    """The reference's record byte string of a 4-bit plane record: row-major codes, low nibble first, then the three
+    fp16 axes."""
+    if record.bits != 4:
+        raise ValueError("plane records are 4-bit")
+    axes = np.concatenate([record.scale_axis, record.zp_axis, record.other_axis]).astype("<u2")
+    return np.concatenate([np.frombuffer(_pack_codes(record.codes), np.uint8), axes.view(np.uint8)])
+
+
+def gvk2_entry(record: Record, iters: int = 0, s_col=None, s_row=None, best_iter: int = 0, best_imbalance: float = 0.0) -> Gvk2Entry:
+    """A GVK2 entry from a plane record that carries its un-quantised values (`orig`, from the stage rows).  With
+    iters = 0 the balancing factors are all ones, as in the reference's iters-0 dumps."""
+    if record.orig is None:
+        raise ValueError("the record has no `orig` block: pass stage_k / stage_v to tile_records")
+    rows, cols = record.codes.shape
+    s_col = np.ones(cols, np.float32) if s_col is None else np.asarray(s_col, np.float32)
+    s_row = np.ones(rows, np.float32) if s_row is None else np.asarray(s_row, np.float32)
+    return Gvk2Entry(record.name, record.bits, iters, best_iter, best_imbalance, s_col, s_row,
+                     np.ascontiguousarray(record.orig, np.float32), record_bytes(record))
+
+
+def write_gvk2(path: str, entries: Sequence[Gvk2Entry]) -> None:
+    with open(path, "wb") as f:
+        f.write(GVK2_MAGIC + struct.pack("<II", 2, len(entries)))
+        for e in entries:
+            name = e.name.encode("utf-8")
+            rows, cols = e.tile.shape
+            f.write(struct.pack("<I", len(name)) + name)
+            f.write(struct.pack("<5i", rows, cols, e.bits, e.iters, e.best_iter))
+            f.write(struct.pack("<f", e.best_imbalance))
+            f.write(np.ascontiguousarray(e.s_col, "<f4").tobytes())
+            f.write(np.ascontiguousarray(e.s_row, "<f4").tobytes())
+            f.write(np.ascontiguousarray(e.tile, "<f4").tobytes())
+            rec = np.ascontiguousarray(e.record, np.uint8)
+            f.write(struct.pack("<I", rec.size) + rec.tobytes())
+
+
+def read_gvk2(path: str) -> List[Gvk2Entry]:
+    b = open(path, "rb").read()
+    if b[:4] != GVK2_MAGIC or struct.unpack_from("<I", b, 4)[0] != 2:
+        raise ValueError("not a GVK2 version 2 file")
+    (n,) = struct.unpack_from("<I", b, 8)
+    o, out = 12, []
+    for _ in range(n):
+        (nl,) = struct.unpack_from("<I", b, o); o += 4
+        name = b[o:o + nl].decode("utf-8"); o += nl
+        rows, cols, bits, iters, best_iter = struct.unpack_from("<5i", b, o); o += 20
+        (imb,) = struct.unpack_from("<f", b, o); o += 4
+        s_col = np.frombuffer(b, "<f4", cols, o).copy(); o += 4 * cols
+        s_row = np.frombuffer(b, "<f4", rows, o).copy(); o += 4 * rows
+        tile = np.frombuffer(b, "<f4", rows * cols, o).reshape(rows, cols).copy(); o += 4 * rows * cols
+        (rl,) = struct.unpack_from("<I", b, o); o += 4
+        rec = np.frombuffer(b, np.uint8, rl, o).copy(); o += rl
+        out.append(Gvk2Entry(name, bits, iters, best_iter, imb, s_col, s_row, tile, rec))
+    if o != len(b):
+        raise ValueError("trailing bytes after the last GVK2 record")
+    return out

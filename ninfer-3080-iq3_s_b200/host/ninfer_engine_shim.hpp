@@ -140,13 +140,26 @@ inline void kvarn128_release_all() {
     detail::layer_states().clear();
 }
 
+// Sinkhorn iterations of the encoder for every layer routed through this shim.  The reference fixes them at compile time,
+// kKvarnIters = 16 (kvarn-port/engine/src/ops/kv_cache/kvarn_layout.h:40-42); that is the default here.  0 selects the
+// regime in which codes are bit-exact against the CPU oracle and the tuned attention kernels apply.  Set it before the
+// first append of a cache: a cache must be read with the iteration count it was written with.
+inline int& kvarn128_sinkhorn_iters() {
+    static int iters = 16;
+    return iters;
+}
+inline void kvarn128_set_sinkhorn_iters(int iters) {
+    if (iters < 0 || iters > 64) throw std::invalid_argument("KVarN128: sinkhorn iterations must be 0..64");
+    kvarn128_sinkhorn_iters() = iters;
+}
+
 namespace detail {
 inline Kvarn128Geometry geometry_of(const Tensor& rows, int q_heads, const Kvarn128LayerState& st) {
     Kvarn128Geometry g;
     g.head_dim = rows.ne[0];
     g.q_heads = q_heads;
     g.dtype = rows.dtype == DType::BF16 ? KVB_DTYPE_BF16 : KVB_DTYPE_F16;
-    g.sinkhorn_iters = 0;
+    g.sinkhorn_iters = kvarn128_sinkhorn_iters();
     g.error_word = st.error_word;
     return g;
 }
@@ -197,11 +210,12 @@ inline void kv_cache_append_launch(const Tensor& k, const Tensor& v, const Tenso
                        "kv_cache_append");
 }
 
-// patches/0003:1397-1428.  valid_columns (masked multi-batch metadata) must be null: one sequence per call.
-inline void kv_cache_append_batch_launch(const Tensor& k, const Tensor& v, const Tensor& positions, const Tensor& valid_columns,
+// patches/0003:1397-1428.  The block table of the sequence is row table_rows[0] of cache.block_tables.  valid_columns
+// selects the masked metadata variant in the reference, but its KvarnTile128 branch takes only tables / table_rows /
+// table_stride from the metadata (patches/0003:1159-1189) and appends all `tokens` rows: the same here.
+inline void kv_cache_append_batch_launch(const Tensor& k, const Tensor& v, const Tensor& positions, const Tensor& /*valid_columns*/,
                                          const Tensor& table_rows, PagedKVBatchLayerView cache, cudaStream_t stream) {
     detail::single_sequence(positions, "kv_cache_append_batch");
-    if (valid_columns.data != nullptr) detail::refuse("kv_cache_append_batch: KVarN128 takes no column mask (single sequence, contiguous positions)");
     const int tokens = k.ne[2];
     if (tokens <= 0) return;
     const Kvarn128LayerView view = detail::layer_view(cache, detail::batch_table(cache.block_tables, table_rows), k, 0, nullptr, 8, stream);
@@ -219,30 +233,41 @@ inline void causal_attention_cached_small_t_launch(const Tensor& q, const Tensor
     causal_attention_cached_small_t_launch(q.data, static_cast<const std::int32_t*>(pos.data), scale, view, st.workspace, out.data, stream);
 }
 
-// patches/0003:3508-3515: verify.  Appends the `width` rows when column_begin == 0 (the reference's rule), then
-// causal attention of those rows.  q: {D, QH, width, 1}; k, v: {D, H, width, 1}.
+// patches/0003:3508-3515: verify.  q: {D, QH, full_width, 1}; k, v: {D, H, full_width, 1}; pos: int32 {full_width}.
+// As in the reference's KvarnTile128 branch (patches/0003:3517-3545): the whole step (all full_width rows) is appended
+// when column_begin == 0; every call then attends the columns [column_begin, column_begin + width) of q, so a step
+// wider than 8 columns is one call with column_begin == 0 followed by calls that only attend.  valid_columns (the
+// count of real columns of a padded step) does not change what is appended there, nor here; the padded columns'
+// outputs are computed like the others and are the caller's to ignore.
 inline void causal_attention_small_t_launch(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& pos,
-                                            const Tensor& valid_columns, const Tensor& table_rows, float scale,
+                                            const Tensor& /*valid_columns*/, const Tensor& table_rows, float scale,
                                             PagedKVBatchLayerView cache, CausalAttentionExecutionEnvelope envelope,
                                             std::int32_t column_begin, std::int32_t width, Tensor& /*partial_acc*/, Tensor& /*partial_m*/,
                                             Tensor& /*partial_l*/, Tensor& out, cudaStream_t stream, const void* /*gate*/ = nullptr) {
     detail::single_sequence(pos, "causal_attention_small_t");
-    if (valid_columns.data != nullptr) detail::refuse("causal_attention_small_t: KVarN128 takes no column mask");
-    if (column_begin != 0) detail::refuse("causal_attention_small_t: KVarN128 appends and attends the whole step at once (column_begin must be 0)");
     if (q.ne[3] != 1) detail::refuse("causal_attention_small_t: one sequence per call");
+    const int full_width = q.ne[2];
+    if (width < 1 || width > 8 || column_begin < 0 || column_begin + width > full_width)
+        detail::refuse("causal_attention_small_t: columns [column_begin, column_begin + width) must lie in the step, width 1..8");
     const Kvarn128LayerView view = detail::layer_view(cache, detail::batch_table(cache.block_tables, table_rows), q, q.ne[1], &envelope, 8, stream);
     const Kvarn128LayerState& st = detail::layer_states()[cache.k_pages.data];
-    causal_attention_small_t_launch(q.data, k.data, v.data, static_cast<const std::int32_t*>(pos.data), scale, view, width, st.workspace,
-                                    out.data, stream);
+    const std::int32_t* positions = static_cast<const std::int32_t*>(pos.data);
+    if (column_begin == 0)
+        detail::raise(kvb_append(&view.layer, k.data, v.data, positions, full_width, stream), "causal_attention_small_t (append)");
+    const std::size_t row_bytes = static_cast<std::size_t>(q.ne[0]) * q.ne[1] * 2;  // fp16 / bf16 rows of all q heads
+    detail::raise(kvb_attn_rows(&view.layer, static_cast<const char*>(q.data) + column_begin * row_bytes, positions + column_begin, width,
+                                positions + (full_width - 1), scale, view.kv_len_max, st.workspace,
+                                static_cast<char*>(out.data) + column_begin * row_bytes, stream),
+                  "causal_attention_small_t");
 }
 
 // patches/0003:2362-2366: prefill chunk.  q: {D, QH, tokens, 1}; k, v: {D, H, tokens, 1}.  `fast` selects between two
-// kernels of equal results in the reference and is ignored here.
+// kernels of equal results in the reference and is ignored here; valid_columns as in kv_cache_append_batch_launch.
 inline void causal_attention_prompt_launch(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& positions,
                                            const Tensor& valid_columns, const Tensor& table_rows, float scale,
                                            PagedKVBatchLayerView cache, Tensor& out, bool /*fast*/, cudaStream_t stream) {
     detail::single_sequence(positions, "causal_attention_prompt");
-    if (valid_columns.data != nullptr) detail::refuse("causal_attention_prompt: KVarN128 takes no column mask");
+    (void)valid_columns;  // as for the append: the reference's KvarnTile128 branch does not read it
     if (q.ne[3] != 1) detail::refuse("causal_attention_prompt: one sequence per call");
     const int tokens = q.ne[2];
     if (tokens <= 0) return;

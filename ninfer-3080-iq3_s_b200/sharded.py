@@ -89,6 +89,40 @@ class ShardedDecode:
         return cache.merge_partials_packed(self.recv, self.world, self.layer.q_heads, self.layer.head_dim, out)
 
 
+class ShardedChunk:
+    """A verify step or a prefill chunk over a sequence whose cache is range-sharded over the ranks of `group`: the new
+    rows are appended on the rank that owns the open tile (the last one), every rank attends its own range
+    (kvb_attn_chunk_partial), one all-gather moves the partials (tokens * q_heads * (head_dim + 2) floats per rank),
+    every rank merges.  `max_tokens` sizes the buffers."""
+
+    def __init__(self, layer, max_tokens: int, group=None):
+        import torch
+        import torch.distributed as dist
+
+        self.layer, self.group = layer, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.per_token = layer.q_heads * (layer.head_dim + 2)
+        self.send = torch.empty(max_tokens * self.per_token, dtype=torch.float32, device=layer.device)
+        self.recv = torch.empty(self.world * max_tokens * self.per_token, dtype=torch.float32, device=layer.device)
+
+    def attend(self, q, k, v, local_positions, scale: float, local_len_max: int, out):
+        """q: [tokens, q_heads, D] (the same on every rank); k, v: the new rows (used on the owner rank only);
+        local_positions: int32 [tokens] on the device -- on the owner the positions of the new rows in its cache, on
+        the other ranks the position of their last token, repeated."""
+        import torch.distributed as dist
+
+        from . import cache
+
+        tokens = int(q.shape[0])
+        n = tokens * self.per_token
+        if self.rank == self.world - 1:
+            self.layer.append(k, v, local_positions)
+        self.layer.attn_chunk_partial_packed(q, local_positions, scale, local_len_max, self.send[:n])
+        dist.all_gather_into_tensor(self.recv[:self.world * n], self.send[:n], group=self.group)
+        return cache.merge_partials_packed(self.recv[:self.world * n], self.world, tokens * self.layer.q_heads, self.layer.head_dim,
+                                           out.view(tokens * self.layer.q_heads, self.layer.head_dim))
+
+
 class PeerRing:
     """Ring buffers for kvb_attn_decode_sharded: one buffer per rank that every rank can write (peer memory).
     `PeerRing.symmetric(...)` allocates it with torch's symmetric memory over the process group (NVLink peer

@@ -359,6 +359,14 @@ static void seal_tile(const kvo_layer* L, int tile, int head) {
     free(rec);
 }
 
+/* Seal tile `tile` of head `head` from whatever the stage slot tile % 2 holds (what a roll-back followed by a
+ * re-seal does, LAUNCH:262-273): lets a test place already-rotated rows in the stage and obtain the planes. */
+void kvo_seal_tile(uint8_t* k_code, uint16_t* k_scale, uint8_t* v_code, uint16_t* v_scale, uint16_t* stage,
+                   const int32_t* table, int head_dim, int kv_heads, int iters, int tile) {
+    kvo_layer L = {k_code, k_scale, v_code, v_scale, stage, table, head_dim, kv_heads, iters};
+    for (int h = 0; h < kv_heads; ++h) seal_tile(&L, tile, h);
+}
+
 /* Append `tokens` contiguous positions pos0.. of one sequence.  k/v: [tok][head][dim] 16-bit,
  * dtype 0 fp16 / 1 bf16.  Tile by tile: rotate the new rows into stage[tile%2], then seal the
  * tile if the append fills it.  LAUNCH:53-77 (tile geometry), :84-120 (rotate), :1066-1092 (loop). */

@@ -1,7 +1,7 @@
 // Compiles the engine-shaped adapter (ninfer::ops launchers over Tensor / PagedKV*LayerView values) and checks the
-// host-side behaviour that needs no GPU: the five launcher signatures exist, multi-sequence positions, column
-// masks and foreign storage kinds are refused with std::invalid_argument before anything is allocated or
-// launched, and empty appends return silently.
+// host-side behaviour that needs no GPU: the five launcher signatures exist; multi-sequence positions, column blocks
+// that leave the step and foreign storage kinds are refused with std::invalid_argument before anything is allocated
+// or launched; empty appends return silently; the encoder's iteration count defaults to the reference's 16.
 #include <cstdio>
 #include <stdexcept>
 
@@ -48,15 +48,18 @@ int main() {
     failures += expect_refusal("append with multi-sequence positions", [&] { kv_cache_append_launch(k, v, pos2, one, nullptr); });
     failures += expect_refusal("prompt with multi-sequence positions",
                                [&] { causal_attention_prompt_launch(q, k, v, pos2, none, rows, 0.1f, many, out, true, nullptr); });
-    // a column mask has no meaning for this cache
-    Tensor mask = pos;
-    failures += expect_refusal("batch append with a column mask", [&] { kv_cache_append_batch_launch(k, v, pos, mask, rows, many, nullptr); });
-    failures += expect_refusal("verify with a column mask", [&] {
-        causal_attention_small_t_launch(q, k, v, pos, mask, rows, 0.1f, many, env, 0, 4, pa, pm, pl, out, nullptr);
-    });
-    failures += expect_refusal("verify with column_begin != 0", [&] {
+    // column blocks must lie inside the step and hold 1..8 columns
+    failures += expect_refusal("verify columns [2, 6) of a 4-column step", [&] {
         causal_attention_small_t_launch(q, k, v, pos, none, rows, 0.1f, many, env, 2, 4, pa, pm, pl, out, nullptr);
     });
+    failures += expect_refusal("verify block of 0 columns", [&] {
+        causal_attention_small_t_launch(q, k, v, pos, none, rows, 0.1f, many, env, 0, 0, pa, pm, pl, out, nullptr);
+    });
+    // the encoder runs the reference's iteration count unless told otherwise
+    if (kvarn128_sinkhorn_iters() != 16) { std::printf("FAIL: default Sinkhorn iterations %d, the reference's are 16\n", kvarn128_sinkhorn_iters()); ++failures; }
+    failures += expect_refusal("65 Sinkhorn iterations", [&] { kvarn128_set_sinkhorn_iters(65); });
+    kvarn128_set_sinkhorn_iters(0);
+    if (kvarn128_sinkhorn_iters() != 0) { std::printf("FAIL: the iteration count did not change\n"); ++failures; }
     // decode takes one token
     failures += expect_refusal("cached decode with 4 tokens",
                                [&] { causal_attention_cached_small_t_launch(q, pos, 0.1f, one, env, pa, pm, pl, out, nullptr); });

@@ -97,3 +97,19 @@ def attn_close(got: np.ndarray, want: np.ndarray, max_abs=ATTN_MAX_ABS, rel_l2=A
     ref = float(np.abs(want).max())
     rel = float(np.sqrt(((got.astype(np.float64) - want) ** 2).sum() / (want.astype(np.float64) ** 2).sum()))
     return err <= max_abs * ref and rel <= rel_l2, f"max-abs {err:.3e} (ref max {ref:.3e}, ratio {err / ref:.2e}), rel-L2 {rel:.2e}"
+
+
+def cpu_twin_of(layer):
+    """A CPU-oracle layer holding the very bytes of a device layer (planes, stage, page table): what the oracle then
+    computes is attention over the cache the GPU kernels read, whoever wrote it."""
+    cpu = orc.CpuLayer(layer.head_dim, layer.kv_heads, layer.pages, layer.table.cpu().numpy(), int(layer.c.sinkhorn_iters))
+    cpu.k_code[:] = layer.k_code.cpu().numpy()
+    cpu.v_code[:] = layer.v_code.cpu().numpy()
+    cpu.k_scale[:] = layer.k_scale.cpu().numpy().view(np.uint16)
+    cpu.v_scale[:] = layer.v_scale.cpu().numpy().view(np.uint16)
+    cpu.stage[:] = layer.stage.cpu().numpy().view(np.uint16).reshape(cpu.stage.shape)
+    return cpu
+
+
+def host_threads():
+    return os.cpu_count() or 1

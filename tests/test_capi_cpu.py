@@ -32,6 +32,21 @@ def test_sizes():
     assert lib.kvb_workspace_bytes(32768, 4, 24, 128, 1, 1) > 0
 
 
+@pytest.mark.parametrize("kv_heads,q_heads,kv_len_max", [(4, 12, 4608), (3, 9, 6144), (7, 21, 2560), (4, 24, 32768), (2, 16, 9000),
+                                                         (1, 7, 12000), (8, 8, 5000), (4, 24, 378944)])
+def test_workspace_covers_every_narrower_call(kv_heads, q_heads, kv_len_max):
+    """A workspace sized for `rows` query tokens must hold every call of 1..rows tokens: the number of splits (hence of
+    partials) is not monotonic in the width, so the size query takes the maximum over the widths."""
+    lib = pkg().capi.load()
+    sizes = [lib.kvb_workspace_bytes(kv_len_max, kv_heads, q_heads, 128, r, 1) for r in range(1, 9)]
+    assert all(a <= b for a, b in zip(sizes, sizes[1:])), sizes
+    G = q_heads // kv_heads
+    for r in range(1, 9):
+        zblocks = (r * G + 15) // 16
+        parts = lib.kvb_split_capacity(kv_len_max, kv_heads, q_heads, r, 1)
+        assert sizes[r - 1] >= kv_heads * zblocks * parts * 16 * (128 + 2) * 4, (r, parts)
+
+
 def _layer(capi, **over):
     L = capi.kvb_layer(k_code=16, k_scale=16, v_code=16, v_scale=16, stage=16, table_direct=16, tables=None,
                        table_rows=None, table_stride=0, table_len=4, pages=4, kv_heads=4, q_heads=24, head_dim=128,

@@ -92,11 +92,45 @@ def test_verify_rows_are_causal(prefix, width):
     tw.len = T
     eq = tw.planes_equal()
     assert all(eq.values()), eq
-    # from 16 GQA-merged rows per KV head on (width >= 3 here) the step runs on the tcgen05 chunk kernel
+    # from 32 GQA-merged rows per KV head on (width >= 6 here) the step runs on the tcgen05 chunk kernel, which rounds
+    # the de-quantised tiles to fp16; narrower steps run on the warp-level kernel and are held to its tolerance
     from helpers import PREFILL_MAX_ABS, PREFILL_REL_L2
-    dense = width * (QH // H) >= 16
+    dense = width * (QH // H) >= 32
     ok, msg = attn_close(out.float().cpu().numpy(), want, PREFILL_MAX_ABS if dense else 2.0 ** -10, PREFILL_REL_L2 if dense else 1e-3)
     assert ok, msg
+
+
+@pytest.mark.parametrize("H,QH,T", [(4, 12, 4600), (3, 9, 6100), (7, 21, 2550)])
+def test_verify_widths_share_one_workspace(H, QH, T):
+    """Three query heads per KV head at 2.5K-6K tokens: a narrow verify step is cut into more splits than a wide one.
+    One workspace sized for width 8 serves every width, canary words behind it stay intact."""
+    import torch
+
+    D = 128
+    tw = Twin(D=D, H=H, QH=QH, capacity_tokens=T + 8, seed=57)
+    k, v = orc.synth_kv(58, T + 8, H, D, 1), orc.synth_kv(58, T + 8, H, D, 2)
+    tw.append(k[:T], v[:T])
+    lib = pkg().capi.load()
+    nbytes = lib.kvb_workspace_bytes(T + 8, H, QH, D, 8, 1)
+    guard = 4096
+    buf = torch.full((nbytes // 4 + guard,), float("nan"), dtype=torch.float32, device=tw.dev)
+    buf[nbytes // 4:] = 12345.0
+    tw.gpu._ws = buf[:nbytes // 4]  # the layer's grow-only workspace: large enough, so it is kept
+    scale = 1.0 / np.sqrt(D)
+    for width in (1, 2, 5, 8, 3):
+        q = orc.synth_q(59 + width, width, QH, D)
+        pos = np.arange(T, T + width, dtype=np.int32)
+        tw.cpu.append(k[T:T + width], v[T:T + width], T)
+        want = tw.cpu.attention(q, pos, scale, QH, threads=4)
+        out = tw.gpu.attn_verify(torch.from_numpy(q).to(tw.dev), torch.from_numpy(k[T:T + width]).to(tw.dev),
+                                 torch.from_numpy(v[T:T + width]).to(tw.dev), torch.from_numpy(pos).to(tw.dev), scale, T + 8)
+        torch.cuda.synchronize()
+        assert tw.gpu._ws.data_ptr() == buf.data_ptr()
+        assert bool((buf[nbytes // 4:] == 12345.0).all()), f"width {width} wrote past its workspace"
+        from helpers import PREFILL_MAX_ABS, PREFILL_REL_L2
+        ok, msg = attn_close(out.float().cpu().numpy(), want, PREFILL_MAX_ABS, PREFILL_REL_L2)
+        assert ok, (width, msg)
+    assert tw.gpu.errors() == 0
 
 
 def test_partials_merge_to_the_full_answer():
@@ -125,6 +159,52 @@ def test_partials_merge_to_the_full_answer():
     assert ok, msg
     full = tw.gpu.attn_decode(qd, pos, scale, T)
     ok, msg = attn_close(full.float().cpu().numpy(), want[0])
+    assert ok, msg
+
+
+@pytest.mark.parametrize("prefix,chunk,cut", [(1000, 4, 512), (1000, 8, 640), (700, 300, 384), (2048, 64, 1024), (300, 3, 256)])
+def test_chunk_partials_of_two_range_caches_merge_to_the_full_answer(prefix, chunk, cut):
+    """A verify step / prefill chunk over a sequence held as two caches (tokens [0, cut) and [cut, ...), the layout of a
+    range-sharded sequence on two GPUs, here side by side on one): the new rows are appended to the second cache, each
+    cache exports its partials (kvb_attn_chunk_partial), the merge equals the oracle's attention over the whole sequence."""
+    import torch
+
+    H, QH, D = 4, 24, 128
+    T = prefix + chunk
+    k, v = orc.synth_kv(71, T, H, D, 1), orc.synth_kv(71, T, H, D, 2)
+    q = orc.synth_q(71, chunk, QH, D)
+    scale = 1.0 / np.sqrt(D)
+    lp = T // 64 + 6
+    cpu = orc.CpuLayer(D, H, lp, orc.shuffled_table(72, lp, lp))
+    cpu.append(k, v, 0)
+    want = cpu.attention(q, np.arange(prefix, T, dtype=np.int32), scale, QH, threads=4)
+    dev = torch.device("cuda:0")
+
+    def cache_of(rows_k, rows_v, seed, room):
+        n = rows_k.shape[0]
+        pages = (n + room + 63) // 64 + 2
+        pages += pages & 1
+        L = pkg().KvarnLayer(D, H, QH, pages, torch.from_numpy(orc.shuffled_table(seed, pages, pages)), device="cuda:0")
+        L.append(torch.from_numpy(rows_k).to(dev), torch.from_numpy(rows_v).to(dev), torch.arange(n, dtype=torch.int32, device=dev))
+        return L
+
+    A = cache_of(k[:cut], v[:cut], 73, 0)
+    B = cache_of(k[cut:prefix], v[cut:prefix], 74, chunk)
+    qd = torch.from_numpy(q).to(dev)
+    pos_b = torch.arange(prefix - cut, T - cut, dtype=torch.int32, device=dev)
+    B.append(torch.from_numpy(k[prefix:]).to(dev), torch.from_numpy(v[prefix:]).to(dev), pos_b)  # the owner of the open tile
+    pos_a = torch.full((chunk,), cut - 1, dtype=torch.int32, device=dev)
+    rows = chunk * QH
+    packed = torch.empty((2, rows * (D + 2)), dtype=torch.float32, device=dev)
+    A.attn_chunk_partial_packed(qd, pos_a, scale, cut, packed[0])
+    B.attn_chunk_partial_packed(qd, pos_b, scale, T - cut, packed[1])
+    out = torch.empty((chunk, QH, D), dtype=torch.float16, device=dev)
+    pkg().cache.merge_partials_packed(packed.view(-1), 2, rows, D, out.view(rows, D))
+    torch.cuda.synchronize()
+    assert A.errors() == 0 and B.errors() == 0
+    from helpers import PREFILL_MAX_ABS, PREFILL_REL_L2
+    dense = chunk > 8 or chunk * (QH // H) >= 32
+    ok, msg = attn_close(out.float().cpu().numpy(), want, PREFILL_MAX_ABS if dense else 2.0 ** -10, PREFILL_REL_L2 if dense else 1e-3)
     assert ok, msg
 
 

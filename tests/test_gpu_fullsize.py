@@ -1,5 +1,7 @@
-"""Size-independent properties at the full size of BASELINE config 4A (one sequence of 378,944 tokens, 24 / 4 heads,
-head_dim 128), where the CPU oracle would take minutes per call:
+"""Full-size cases (one sequence of 378,944 tokens; a 1,024-token chunk over 262,144 tokens; verify steps over 131,072
+tokens; 32 sequences of 16K..131K tokens; 24 / 4 heads, head_dim 128).  Each compares sampled rows with the CPU
+oracle run over the very bytes the GPU wrote (the planes are copied into an oracle layer), and keeps the
+size-independent properties:
   * the planes do not depend on how the tokens were chunked into appends, nor on where the pages lie: two caches
     with different page tables, filled in chunks of 8,192 and of 4,099 tokens, hold the same bytes page for page;
   * decode attention is bit-identical on the two caches (same logical content, different physical placement);
@@ -9,7 +11,8 @@ head_dim 128), where the CPU oracle would take minutes per call:
 import numpy as np
 import pytest
 
-from helpers import pkg
+from helpers import (ATTN_MAX_ABS, ATTN_REL_L2, PREFILL_MAX_ABS, PREFILL_REL_L2, attn_close, cpu_twin_of, host_threads,
+                     orc, pkg)
 
 pytestmark = pytest.mark.gpu
 
@@ -62,6 +65,12 @@ def test_config_4a_properties():
     torch.cuda.synchronize()
     assert torch.isfinite(full_a.float()).all()
     assert torch.equal(full_a, full_b)
+    # the oracle over the same bytes: the whole decode row at 378,944 tokens, and its partials over eight ranges
+    cpu = cpu_twin_of(A)
+    qn = q.cpu().numpy()[None]
+    want = cpu.attention(qn, [T - 1], scale, QH, threads=host_threads(), kv_total=T)[0]
+    ok, msg = attn_close(full_a.float().cpu().numpy(), want, ATTN_MAX_ABS, ATTN_REL_L2)
+    assert ok, msg
     # eight tile-aligned key ranges -> partials -> merge
     tiles = (T + 127) // 128
     ms, ls, os_ = [], [], []
@@ -70,6 +79,8 @@ def test_config_4a_properties():
         m, l, o = A.attn_decode_partial(q, pos, scale, T, key_begin=b, key_end=e)
         ms.append(m.clone()); ls.append(l.clone()); os_.append(o.clone())
     merged = pkg().cache.merge_partials(torch.stack(ms), torch.stack(ls), torch.stack(os_))
+    ok, msg = attn_close(merged.float().cpu().numpy(), want, ATTN_MAX_ABS, ATTN_REL_L2)
+    assert ok, "eight ranges merged vs oracle: " + msg
     ref = full_a.float()
     tol = 2.0 ** -10 * ref.abs().max().item()
     assert (merged.float() - ref).abs().max().item() <= tol
@@ -80,7 +91,7 @@ def test_config_4a_properties():
 
 
 def test_config_3_chunk_rows_equal_single_row_decodes():
-    """BASELINE config 3 at full size (1,024-token chunk over a 262,144-token prefix): every row of a causal chunk
+    """Full size (a 1,024-token chunk over a 262,144-token prefix): rows 0, 500 and 1,023 against the oracle; and every row of a causal chunk
     attention is the decode attention of that row alone over the keys it may see.  Rows 0, 500 and 1,023 of the
     tensor-core chunk kernel against the warp-level decode kernel on the same cache (two independent kernels),
     within the chunk kernel's tolerance."""
@@ -108,6 +119,13 @@ def test_config_3_chunk_rows_equal_single_row_decodes():
     out = L.attn_prefill(q, k, v, pos, scale, prefix + chunk)
     torch.cuda.synchronize()
     assert L.errors() == 0 and torch.isfinite(out.float()).all()
+    sample = [0, 500, chunk - 1]
+    cpu = cpu_twin_of(L)
+    want = cpu.attention(q[sample].cpu().numpy(), [prefix + i for i in sample], scale, QH, threads=host_threads(),
+                         kv_total=prefix + chunk)
+    for j, i in enumerate(sample):
+        ok, msg = attn_close(out[i].float().cpu().numpy(), want[j], PREFILL_MAX_ABS, PREFILL_REL_L2)
+        assert ok, f"chunk row {i} vs oracle: {msg}"
     for i in (0, 500, chunk - 1):
         ref = L.attn_decode(q[i], pos[i:i + 1], scale, prefix + chunk).float()
         got = out[i].float()
@@ -117,7 +135,7 @@ def test_config_3_chunk_rows_equal_single_row_decodes():
 
 
 def test_config_2_verify_rows_equal_single_row_decodes():
-    """BASELINE config 2 at full size (131,072-token prefix, 4 and 8 draft rows): row i of a verify step equals the
+    """Full size (verify steps of 4 and 8 draft rows over a 131,072-token prefix): every row against the oracle; and row i of a verify step equals the
     decode of row i alone; width 4 runs on the warp-level kernel, width 8 on the tensor-core chunk kernel.  The
     second step re-appends at the same positions (the drafts of the first were rolled back)."""
     import torch
@@ -143,6 +161,13 @@ def test_config_2_verify_rows_equal_single_row_decodes():
         pos = torch.arange(prefix, prefix + width, dtype=torch.int32, device=dev)
         out = L.attn_verify(q, k, v, pos, scale, prefix + 8)
         torch.cuda.synchronize()
+        # every row against the oracle over the bytes this step left in the cache (its new rows are in the stage)
+        dense = width * (QH // H) >= 32  # the tcgen05 chunk kernel rounds the de-quantised tiles to fp16
+        want = cpu_twin_of(L).attention(q.cpu().numpy(), pos.cpu().numpy(), scale, QH, threads=host_threads(),
+                                        kv_total=prefix + width)
+        ok, msg = attn_close(out.float().cpu().numpy(), want, PREFILL_MAX_ABS if dense else ATTN_MAX_ABS,
+                             PREFILL_REL_L2 if dense else ATTN_REL_L2)
+        assert ok, f"width {width} vs oracle: {msg}"
         for i in range(width):
             ref = L.attn_decode(q[i], pos[i:i + 1], scale, prefix + 8).float()
             got = out[i].float()
@@ -152,8 +177,8 @@ def test_config_2_verify_rows_equal_single_row_decodes():
 
 
 def test_config_4b_batched_decode_equals_one_call_per_sequence():
-    """BASELINE config 4B at full size: 32 sequences of 16,384 .. 131,072 tokens, one kvb_attn_decode_batch call
-    against one kvb_attn_decode per sequence (same kernels, different cuts of the keys)."""
+    """Full size (32 sequences of 16,384 .. 131,072 tokens): one kvb_attn_decode_batch call against the oracle on three
+    sequences, and against one kvb_attn_decode per sequence (same kernels, different cuts of the keys)."""
     import random
 
     import torch
@@ -187,6 +212,12 @@ def test_config_4b_batched_decode_equals_one_call_per_sequence():
     # a head (it shows up in dim 0 after the inverse rotation).  An output here is the average of 10^5 random values,
     # about 0.02, so the noise is judged against the scale of V itself: below 2^-13 of the largest |V|.
     vmax = pool_v.float().abs().max().item()
+    order = sorted(range(32), key=lambda i: lengths[i])
+    for i in (order[0], order[16], order[-1]):  # shortest, a middle one, longest: the batched call against the oracle
+        want_i = cpu_twin_of(layers[i]).attention(q[i].cpu().numpy()[None], [lengths[i] - 1], scale, QH,
+                                                  threads=host_threads(), kv_total=lengths[i])[0]
+        ok, msg = attn_close(out[i].cpu().numpy(), want_i, ATTN_MAX_ABS, ATTN_REL_L2)
+        assert ok, f"sequence {i} ({lengths[i]} tokens) vs oracle: {msg}"
     for i in range(32):
         assert (out[i] - want[i]).abs().max().item() <= 2.0 ** -13 * vmax, i
         assert ((out[i] - want[i]).norm() / want[i].norm()).item() <= 5e-3, i

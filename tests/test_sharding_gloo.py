@@ -32,7 +32,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, T, ret):
+def _worker(rank, world, port, T, ret, rows=1):
     import torch
     import torch.distributed as dist
 
@@ -42,40 +42,50 @@ def _worker(rank, world, port, T, ret):
     sh = pkg().sharded
     D, H, QH = 128, 4, 24
     k, v = orc.synth_kv(80, T, H, D, 1), orc.synth_kv(80, T, H, D, 2)
-    q = orc.synth_q(80, 1, QH, D)
-    b, e = sh.tile_ranges(T, world)[rank]
+    q = orc.synth_q(80, rows, QH, D)
+    T -= rows - 1  # the last `rows` tokens are the query rows of a verify step: row i sees keys 0 .. T - 1 + i
+    b, e = sh.tile_ranges(T + rows - 1, world)[rank]
     n = e - b
     lp = n // 64 + 4
     local = orc.CpuLayer(D, H, lp, orc.shuffled_table(rank, lp, lp))
     if n:
         local.append(k[b:e], v[b:e], 0)
     scale = 1.0 / np.sqrt(D)
+    # positions in the local cache: the owner of the open tile (last rank) holds the query rows' own keys, the
+    # other ranks see all of their range
+    if rank == world - 1:
+        lpos = np.arange(n - rows, n, dtype=np.int32)
+    else:
+        lpos = np.full(rows, n - 1, np.int32)
     if n:
-        _, m, l, o = local.attention(q, [n - 1], scale, QH, want_partials=True)
+        _, m, l, o = local.attention(q, lpos, scale, QH, want_partials=True)
     else:  # a rank without keys contributes the neutral partial
-        m = np.full((1, QH), -np.inf, np.float32); l = np.zeros((1, QH), np.float32); o = np.zeros((1, QH, D), np.float32)
-    packed = sh.pack_partial(torch.from_numpy(m[0]), torch.from_numpy(l[0]), torch.from_numpy(o[0]))
+        m = np.full((rows, QH), -np.inf, np.float32); l = np.zeros((rows, QH), np.float32); o = np.zeros((rows, QH, D), np.float32)
+    packed = sh.pack_partial(torch.from_numpy(m.reshape(-1)), torch.from_numpy(l.reshape(-1)), torch.from_numpy(o.reshape(-1, D)))
     gathered = sh.all_gather_partials(packed)
     gm, gl, go = sh.unpack_partials(gathered)
     merged = orc.merge_partials(gm.numpy(), gl.numpy(), go.numpy())
     if rank == 0:
-        full = orc.CpuLayer(D, H, T // 64 + 4, orc.shuffled_table(9, T // 64 + 4, T // 64 + 4))
+        total = T + rows - 1
+        full = orc.CpuLayer(D, H, total // 64 + 4, orc.shuffled_table(9, total // 64 + 4, total // 64 + 4))
         full.append(k, v, 0)
-        want = full.attention(q, [T - 1], scale, QH)[0]
+        want = full.attention(q, np.arange(total - rows, total, dtype=np.int32), scale, QH).reshape(rows * QH, D)
         ret.put(float(np.abs(merged - want).max() / np.abs(want).max()))
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("T", [1000, 100])
-def test_range_sharded_decode_world2(T):
+@pytest.mark.parametrize("T,rows", [(1000, 1), (100, 1), (1000, 5), (300, 8)])
+def test_range_sharded_decode_world2(T, rows):
+    """rows = 1: decode.  rows > 1: a verify step whose rows are the last tokens of the sequence (the same partition /
+    all-gather / merge with tokens * q_heads rows per rank, what kvb_attn_chunk_partial feeds on GPUs)."""
     import torch.multiprocessing as mp
 
     pkg()
     ctx = mp.get_context("spawn")
     ret = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, T, ret)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, T, ret, rows)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
