@@ -1,16 +1,17 @@
 // kvb_attn.cu -- paged split-K attention over the quantised cache for 1..8 query tokens (decode, MTP
 // verify), de-quantisation fused into the QK and PV loops.  head_dim 128.
 //
-// Grid (splits, kv heads, row blocks).  A CTA owns one KV head, one contiguous range of sealed tiles (128
-// tokens = two pages) and a block of up to 16 GQA-merged query rows (row = token * G + q head within the KV
-// head); the last split of a head also reads the open tile, whose rows are still un-quantised fp16 in the
-// stage.  Inside a CTA each of the 12 warps streams its own sub-range of tiles through a private ring of six
-// 2 KB slots in shared memory filled by bulk async copies (one mbarrier per slot).  A tile arrives as a header
-// (the K scale page and the two V scale pages, double-buffered) followed by eight chunks of 32 keys: four of
-// K codes, then four of V codes; a slot is refilled as soon as its chunk has been consumed, so five sixths of
-// a warp's ring are in flight at any time and warps never synchronise with each other until the final merge.
+// Grid (splits, kv heads, row blocks).  A CTA owns one KV head, one contiguous range of sealed pages and a block
+// of up to 16 GQA-merged query rows (row = token * G + q head within the KV head); the last split of a head also
+// reads the open tile, whose rows are still un-quantised fp16 in the stage.  Inside a CTA each of the 12 warps
+// streams its own sub-range of pages through a private ring of three 4 KB slots in shared memory filled by bulk
+// async copies (one mbarrier per slot) and never synchronises with another warp until the final merge.  A page
+// arrives as two chunks: its K codes together with a small header (the page's V scale rows; its K scale rows when
+// it is the first page of a tile the warp sees), then its V codes as four 1 KB sub-blocks, each shifted 16 bytes
+// further, which makes the transposing ldmatrix reads of the V codes free of bank conflicts.  A slot is refilled
+// as soon as its chunk has been consumed, so two thirds of a warp's ring are in flight at any time.
 //
-// Math per tile (quantised-domain identities, no per-element de-quantisation), all on the int8 tensor path:
+// Math per page (quantised-domain identities, no per-element de-quantisation), all on the int8 tensor path:
 //   logit[r][j] = sum_d (q'[r][d] * scale_K[d]) * code_K[j][d]  +  sum_d q'[r][d] * zp_K[d]
 //   o[r][d]    += sum_j (p[r][j] * scale_V[j]) * code_V[j][d]   +  sum_j p[r][j] * zp_V[j]
 // with q' = H q * softmax_scale * log2(e).  Both contractions are mma.sync m16n8k32 (u8 x s8/u8 -> s32) with
@@ -18,11 +19,11 @@
 //   * QK: q' * scale_K is quantised per query row to 16 bits = a signed high and an unsigned low byte; the
 //     packed code bytes feed the MMA as they lie in the page (byte & 0x0F = even dim, byte & 0xF0 = 16 x odd
 //     dim), the four integer partial sums recombine exactly in int32.
-//   * PV: p (relative to the row maximum of THIS tile, so p <= 1) times scale_V is quantised to 16 bits = two
+//   * PV: p (relative to the row maximum of THIS page, so p <= 1) times scale_V is quantised to 16 bits = two
 //     unsigned bytes; V codes are transposed to "four keys of one dim per register" by ldmatrix.trans plus one
-//     byte permute and one AND per register; the integer sums of the tile are converted once per tile and
-//     enter the running fp32 accumulators with the weight exp2(tile max - running max).
-// The tile-local reference keeps 16 significant bits below each tile's own maximum, whatever the global one is.
+//     byte permute and one AND per register; the integer sums of the page are converted once per page and
+//     enter the running fp32 accumulators with the weight exp2(page max - running max).
+// The page-local reference keeps 16 significant bits below each page's own maximum, whatever the global one is.
 #include <algorithm>
 #include <climits>
 #include <cstddef>
@@ -34,17 +35,19 @@ namespace kvb {
 namespace {
 
 constexpr int D = 128;
-constexpr int kWarpsDecode = 12;    // warps per CTA for up to 8 merged query rows (one N block per warp)
-constexpr int kWarpsWide = 8;       // ... for 9..16 merged rows (two N blocks per warp: twice the accumulators)
+constexpr int kWarpsDecode = 12;    // warps per CTA for up to 8 merged query rows (one N block per warp): 168 registers per thread
+constexpr int kWarpsWide = 8;       // ... for 9..16 merged rows (two N blocks per warp: twice the accumulators): 255 registers
 constexpr int kRows = 16;           // query rows per CTA: one or two 8-row N blocks
-constexpr int kChunkKeys = 32;      // keys per ring slot
-constexpr int kChunkBytes = kChunkKeys * (D / 2);  // 2048: the K or the V codes of 32 keys
-constexpr int kSlots = 6;           // ring slots per warp
-constexpr int kHdrK = 640, kHdrV = 512, kHdrBytes = kHdrK + 2 * kHdrV;  // K scale page (first page of the tile), V scale pages
-constexpr int kScratchBytes = 256 + 256 + 128;  // per warp: scale_K[128], zp_K[128], other_K[64] as fp16
+constexpr int kChunkBytes = kPage * (D / 2);  // 4096: the K or the V codes of one page
+constexpr int kVSub = 1024 + 16;    // V codes lie as four sub-blocks of 16 keys, sub-block a at a * kVSub: key k at k * 64 + 16 * (k / 16)
+constexpr int kSlotBytes = 4224;    // 4096 + 48 bytes of sub-block shifts, rounded up to 128
+constexpr int kSlots = 3;           // ring slots per consumer warp
+constexpr int kHdrs = 3;            // header buffers per consumer (a header lives from the issue of its page's K chunk to the end of the page)
+constexpr int kHdrV = 512, kHdrK = 640, kHdrBytes = kHdrV + kHdrK;  // V scale rows of the page, then (first page of a tile) the K scale rows
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kMagic = 12582912.0f;   // 1.5 * 2^23: x + kMagic has round(x) in its low mantissa bits (|x| < 2^22)
 constexpr float kPMax = 65000.0f;       // largest 16-bit weight (a margin below 65535 absorbs the rounding of the factor)
+constexpr int kTabPad = 4;          // the per-dim tables are padded by 4 floats per 32 dims: the four 32-dim chunks a warp reads at once fall in different banks
 
 struct AttnParams {
     LayerView L;
@@ -61,11 +64,10 @@ struct AttnParams {
 };
 
 struct __align__(128) WarpRing {
-    uint8_t slots[kSlots][kChunkBytes];
-    uint8_t hdr[2][kHdrBytes];
-    uint8_t scratch[kScratchBytes];
-    uint64_t bars[kSlots];
-    uint64_t hbars[2];
+    uint8_t slots[kSlots][kSlotBytes];
+    uint8_t hdr[kHdrs][kHdrBytes];
+    float scale_k[D + 4 * kTabPad], zp_k[D + 4 * kTabPad];  // per-dim scale / zero point of K for the tile in work: dim d at d + kTabPad * (d / 32)
+    uint64_t bars[kSlots];      // completes when the copies of the chunk in the slot have landed
 };
 
 template <int W> struct __align__(128) AttnSmem {
@@ -113,6 +115,20 @@ __device__ __forceinline__ void imma_uu(int (&d)[4], uint32_t a0, uint32_t a1, u
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The same with a zero accumulator: starts a sum without a register clear.
+__device__ __forceinline__ void imma_us0(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void imma_uu0(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 // Q-side fragments for the open tile from q' (shared memory, fragment order).  Lane (g, t) prepares row 8 nb + g, dims
 // 32t .. 32t+31 in natural pairs (2e, 2e+1), split into an fp16 high and low part so the product keeps fp32 accuracy.
 template <int NB, typename Smem>
@@ -147,7 +163,7 @@ template <int NB> struct QInt {
 };
 
 template <int NB, typename Smem>
-__device__ __forceinline__ void build_qint(const Smem& sm, const uint8_t* scratch, int lane, QInt<NB>& f) {
+__device__ __forceinline__ void build_qint(const Smem& sm, const WarpRing& R, int lane, QInt<NB>& f) {
     const int t = lane & 3;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
@@ -156,14 +172,12 @@ __device__ __forceinline__ void build_qint(const Smem& sm, const uint8_t* scratc
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float4 qv = sm.qfrag[nb][j][lane];
-            const uint2 ks = *reinterpret_cast<const uint2*>(scratch + (32 * t + 4 * j) * 2);
-            const uint2 kz = *reinterpret_cast<const uint2*>(scratch + 256 + (32 * t + 4 * j) * 2);
-            const float2 s01 = unpack_half2(ks.x), s23 = unpack_half2(ks.y);
-            const float2 z01 = unpack_half2(kz.x), z23 = unpack_half2(kz.y);
-            qs[4 * j + 0] = qv.x * s01.x; qs[4 * j + 1] = qv.y * s01.y;
-            qs[4 * j + 2] = qv.z * s23.x; qs[4 * j + 3] = qv.w * s23.y;
-            qz = fmaf(qv.x, z01.x, qz); qz = fmaf(qv.y, z01.y, qz);
-            qz = fmaf(qv.z, z23.x, qz); qz = fmaf(qv.w, z23.y, qz);
+            const float4 ks = *reinterpret_cast<const float4*>(&R.scale_k[(32 + kTabPad) * t + 4 * j]);
+            const float4 kz = *reinterpret_cast<const float4*>(&R.zp_k[(32 + kTabPad) * t + 4 * j]);
+            qs[4 * j + 0] = qv.x * ks.x; qs[4 * j + 1] = qv.y * ks.y;
+            qs[4 * j + 2] = qv.z * ks.z; qs[4 * j + 3] = qv.w * ks.w;
+            qz = fmaf(qv.x, kz.x, qz); qz = fmaf(qv.y, kz.y, qz);
+            qz = fmaf(qv.z, kz.z, qz); qz = fmaf(qv.w, kz.w, qz);
             amax = fmaxf(fmaxf(amax, fmaxf(fabsf(qs[4 * j]), fabsf(qs[4 * j + 1]))), fmaxf(fabsf(qs[4 * j + 2]), fabsf(qs[4 * j + 3])));
         }
         qz += __shfl_xor_sync(0xffffffffu, qz, 1);
@@ -192,15 +206,16 @@ __device__ __forceinline__ void build_qint(const Smem& sm, const uint8_t* scratc
     }
 }
 
-// Scale page of K -> warp scratch in natural dim order.  A page row is 5 halves
-// [scale(2r) scale(2r+1) zp(2r) zp(2r+1) other(r)]; lane l re-packs rows 2l and 2l+1 (20 bytes).
-__device__ __forceinline__ void transpose_k_scale(const uint8_t* kscale_page, uint8_t* scratch, int lane) {
-    const uint32_t* w = reinterpret_cast<const uint32_t*>(kscale_page + 20 * lane);
+// Scale rows of K -> per-dim tables in natural dim order, fp32.  A page row is 5 halves
+// [scale(2r) scale(2r+1) zp(2r) zp(2r+1) other(r)]; lane l converts rows 2l and 2l+1 (20 bytes): dims 4l .. 4l+3.
+__device__ __forceinline__ void transpose_k_scale(const uint8_t* kscale_rows, WarpRing& R, int lane) {
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(kscale_rows + 20 * lane);
     const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3], w4 = w[4];
     // halves: w0 = s(4l) s(4l+1) | w1 = z(4l) z(4l+1) | w2 = o(2l) s(4l+2) | w3 = s(4l+3) z(4l+2) | w4 = z(4l+3) o(2l+1)
-    *reinterpret_cast<uint2*>(scratch + 8 * lane) = make_uint2(w0, prmt(w2, w3, 0x5432));
-    *reinterpret_cast<uint2*>(scratch + 256 + 8 * lane) = make_uint2(w1, prmt(w3, w4, 0x5432));
-    *reinterpret_cast<uint32_t*>(scratch + 512 + 4 * lane) = prmt(w2, w4, 0x7610);
+    const float2 s01 = unpack_half2(w0), s23 = unpack_half2(prmt(w2, w3, 0x5432));
+    const float2 z01 = unpack_half2(w1), z23 = unpack_half2(prmt(w3, w4, 0x5432));
+    *reinterpret_cast<float4*>(&R.scale_k[4 * lane + kTabPad * (lane >> 3)]) = make_float4(s01.x, s01.y, s23.x, s23.y);
+    *reinterpret_cast<float4*>(&R.zp_k[4 * lane + kTabPad * (lane >> 3)]) = make_float4(z01.x, z01.y, z23.x, z23.y);
 }
 
 // Running maximum moves to mnew: rescale the accumulators of one row pair.  alpha = exp2(m_old - m_new).
@@ -306,16 +321,16 @@ __device__ __forceinline__ void process_stage_group(const __half* krow, const __
 }
 
 // The work of one CTA: split `split` of KV head `head`, row block `zb`; its partial goes to rows pidx .. pidx + 15 of
-// the workspace.  NB = 8-row blocks of query rows; a pass = the keys whose logits are held at once (a whole tile for
-// NB = 1, one page for NB = 2).
+// the workspace.  NB = 8-row blocks of query rows per warp.  A pass = one page: its 64 logits per row are held at
+// once.  Within a page the keys are taken in a fixed permutation (see key_lo below) that lets the QK accumulators
+// feed the PV operands of the shifted V sub-blocks without any re-ordering.
 template <int NB, int W>
 __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int head, int zb, int64_t pidx) {
     constexpr int kWarps = W, kThreads = W * 32;
-    constexpr int kPassKeys = NB == 1 ? 128 : 64;
-    constexpr int kPasses = kTile / kPassKeys;     // passes per tile
-    constexpr int kPassChunks = kPassKeys / kChunkKeys;  // K chunks (= V chunks) per pass
-    constexpr int kPassGroups = kPassKeys / 16;
-    constexpr int kDimSweeps = NB;                 // the V chunks of a pass are swept once per 128 / NB dims
+    constexpr int kGroups = kPage / 16;            // 16-key groups of a page
+    constexpr int kDimSweeps = NB;                 // the V chunk of a page is swept once per 128 / NB dims
+    constexpr int kORow = D + 4, kWarpFloats = 3 * kRows + kRows * kORow;  // merge buffer of a warp: m, l, z per row, then o
+    static_assert(kWarps * kWarpFloats * 4 <= static_cast<int>(sizeof(WarpRing)) * kWarps, "merge buffer exceeds the rings");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     AttnSmem<W>& sm = *reinterpret_cast<AttnSmem<W>*>(smem_raw);
     const LayerView& L = P.L;
@@ -323,15 +338,18 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
     const int G = L.q_heads / L.kv_heads;
     WarpRing& R = sm.ring[warp];
     // ---- order of the first memory requests: the few bytes everything waits for (positions, q rows, page table
-    //      entries) go out first, then the first chunks of every warp, then -- after the rotation of q -- the rest of
+    //      entries) go out first, then the first chunk of every warp, then -- after the rotation of q -- the rest of
     //      the ring.
-    uint16_t qraw[2][4];
-    int qpos[2] = {-1, -1};
+    constexpr int kQIter = (8 * NB + W - 1) / W;  // warp w prepares rows w, w + W, ... of the block
+    uint16_t qraw[kQIter][4];
+    int qpos[kQIter];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {  // warps 0..7 prepare rows w and w + 8 of the block
+    for (int i = 0; i < kQIter; ++i) {
         qraw[i][0] = qraw[i][1] = qraw[i][2] = qraw[i][3] = 0;
-        if (i < NB && warp < 8) {
-            const int Rr = zb * kRows + warp + 8 * i, tq = Rr / G, gq = Rr % G;
+        qpos[i] = -1;
+        const int r = warp + W * i;
+        if (r < 8 * NB) {
+            const int Rr = zb * kRows + r, tq = Rr / G, gq = Rr % G;
             if (tq < P.T) {
                 const uint16_t* qrow = P.q + (static_cast<int64_t>(tq) * L.q_heads + head * G + gq) * D;
 #pragma unroll
@@ -342,85 +360,81 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
     }
     const int kv_total = *P.total_pos + 1;
     const int key_end = min(P.key_end, kv_total), key_begin = max(P.key_begin, 0);
-    const int sealed_tiles = kv_total / kTile;
+    const int sealed_pages = 2 * (kv_total / kTile);
 
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < kSlots; ++s) mbar_init(&R.bars[s], 1);
-        mbar_init(&R.hbars[0], 1);
-        mbar_init(&R.hbars[1], 1);
         mbar_fence_init();
     }
     __syncwarp();
-    const int32_t* tbl = L.table();
-    // tiles of this CTA, then of this warp
+    // pages of this CTA, then of this warp
     int w0, w1;
     {
-        const int tb = min(key_begin / kTile, sealed_tiles), te = min((key_end + kTile - 1) / kTile, sealed_tiles);
-        const int n = max(te - tb, 0);
-        const int c0 = tb + static_cast<int>(static_cast<int64_t>(n) * split / P.nsplit);
-        const int c1 = tb + static_cast<int>(static_cast<int64_t>(n) * (split + 1) / P.nsplit);
+        const int pb = min(key_begin / kPage, sealed_pages), pe = min((key_end + kPage - 1) / kPage, sealed_pages);
+        const int n = max(pe - pb, 0);
+        const int c0 = pb + static_cast<int>(static_cast<int64_t>(n) * split / P.nsplit);
+        const int c1 = pb + static_cast<int>(static_cast<int64_t>(n) * (split + 1) / P.nsplit);
         w0 = c0 + (c1 - c0) * warp / kWarps;
         w1 = c0 + (c1 - c0) * (warp + 1) / kWarps;
     }
-    const int ntiles = w1 - w0, nchunks = 8 * ntiles;
-    // Page table entries are read 32 at a time, one per lane, a full batch ahead of their use: lane l of `ids`
-    // knows the physical page of logical page ids_base + l, `ids_next` the 32 after those.
-    int ids_base = 2 * w0;
-    auto load_ids = [&](int base) -> int32_t { return base + lane < 2 * w1 ? L.page_of(tbl, base + lane) : -1; };
-    int32_t ids = ntiles > 0 ? load_ids(ids_base) : -1, ids_next = ntiles > 0 ? load_ids(ids_base + 32) : -1;
-    auto page_id = [&](int lp) -> int32_t {  // whole warp; lp in [ids_base, ids_base + 64)
-        const int k = lp - ids_base;
-        const int32_t a = __shfl_sync(0xffffffffu, ids, k & 31), b = __shfl_sync(0xffffffffu, ids_next, k & 31);
-        return k < 32 ? a : b;
-    };
-    // chunk n of this warp: tile w0 + n / 8; within the tile the chunks come in consumption order
-    auto chunk_src = [&](int n, int& lp, int& is_v, int& half) {
-        const int j = n & 7;
-        int page;
-        if constexpr (kPasses == 1) { is_v = j >> 2; page = (j >> 1) & 1; }
-        else { page = j >> 2; is_v = (j >> 1) & 1; }
-        half = j & 1;
-        lp = 2 * (w0 + (n >> 3)) + page;
-    };
-    uint32_t bad_chunks = 0;  // bit s: the chunk now assigned to slot s has no valid page (bad table entry): skip it
-    auto issue_chunk = [&](int n, int slot) {  // whole warp (page id by shuffle); lane 0 issues
-        int lp, is_v, half;
-        chunk_src(n, lp, is_v, half);
-        const int32_t page = page_id(lp);
-        if (page < 0) { bad_chunks |= 1u << slot; return; }
-        bad_chunks &= ~(1u << slot);
-        if (lane == 0) {
-            const uint8_t* src = (is_v ? L.v_code : L.k_code) + page_head_offset(64, L.kv_heads, page, head) + half * kChunkBytes;
-            mbar_expect_tx(&R.bars[slot], kChunkBytes);
-            bulk_g2s(R.slots[slot], src, kChunkBytes, &R.bars[slot]);
-        }
-    };
-    uint32_t bad_hdr = 0;
-    auto issue_header = [&](int ti) {  // whole warp
-        const int32_t p0 = page_id(2 * (w0 + ti)), p1 = page_id(2 * (w0 + ti) + 1);
-        const int hb = ti & 1;
-        if (p0 < 0 || p1 < 0) { bad_hdr |= 1u << hb; return; }
-        bad_hdr &= ~(1u << hb);
-        if (lane == 0) {
-            uint8_t* dst = R.hdr[hb];
-            mbar_expect_tx(&R.hbars[hb], kHdrBytes);
-            bulk_g2s(dst, L.k_scale + page_head_offset(5, L.kv_heads, p0, head), kHdrK, &R.hbars[hb]);
-            bulk_g2s(dst + kHdrK, L.v_scale + page_head_offset(4, L.kv_heads, p0, head), kHdrV, &R.hbars[hb]);
-            bulk_g2s(dst + kHdrK + kHdrV, L.v_scale + page_head_offset(4, L.kv_heads, p1, head), kHdrV, &R.hbars[hb]);
-        }
-    };
+    const int npages = w1 - w0, nchunks = 2 * npages;
+    // ---- the refill side of the ring.  Chunk n of this warp is page w0 + n / 2: even n = K codes + header, odd n = V
+    //      codes.  Page table entries are read 32 at a time, one per lane, a batch ahead of the chunk being issued (the
+    //      only place page ids are needed): lane l of `ids` knows logical page ids_base + l, `ids_next` the 32 after.
+    //      A page whose table entry is bad (-1) gets no copies and its pass is skipped; the error word says why.
+    const int32_t* tbl = L.table();
+    auto load_ids = [&](int base) -> int32_t { return base + lane < w1 ? L.page_of(tbl, base + lane) : -1; };
+    int ids_base = w0;
+    int32_t ids = npages > 0 ? load_ids(ids_base) : -1, ids_next = npages > 0 ? load_ids(ids_base + 32) : -1;
+    // byte offsets of this head inside a page of each plane, and the planes' page strides
+    const uint32_t code_stride = static_cast<uint32_t>(L.kv_heads) * kChunkBytes;
+    const uint8_t* const kc = L.k_code + static_cast<size_t>(head) * kChunkBytes;
+    const uint8_t* const vc = L.v_code + static_cast<size_t>(head) * kChunkBytes;
+    const uint8_t* const ksr = reinterpret_cast<const uint8_t*>(L.k_scale) + static_cast<size_t>(head) * kHdrK;
+    const uint8_t* const vsr = reinterpret_cast<const uint8_t*>(L.v_scale) + static_cast<size_t>(head) * kHdrV;
+    uint32_t live = 0;       // bit s: a copy is in flight into / has landed in slot s
+    int32_t issue_pid = -1;  // page id of the page whose K chunk was issued last (its V chunk comes next)
     int n_issued = 0;
-    if (ntiles > 0) {
-        issue_header(0);
-        for (; n_issued < 2 && n_issued < nchunks; ++n_issued) issue_chunk(n_issued, n_issued);
-    }
+    auto issue_next = [&](int slot) {  // whole warp; chunk n_issued goes into `slot`
+        const int n = n_issued++;
+        if ((n & 1) == 0) {
+            const int lp = w0 + (n >> 1);
+            if (lp - ids_base == 32) {
+                ids = ids_next;
+                ids_base += 32;
+                ids_next = load_ids(ids_base + 32);
+            }
+            issue_pid = __shfl_sync(0xffffffffu, ids, lp - ids_base);
+        }
+        const int32_t pid = issue_pid;
+        if (pid < 0) { live &= ~(1u << slot); return; }
+        live |= 1u << slot;
+        if (lane == 0) {
+            uint8_t* dst = R.slots[slot];
+            if (n & 1) {
+                const uint8_t* src = vc + static_cast<size_t>(pid) * code_stride;
+                mbar_expect_tx(&R.bars[slot], kChunkBytes);
+#pragma unroll
+                for (int a = 0; a < 4; ++a) bulk_g2s(dst + a * kVSub, src + a * 1024, 1024, &R.bars[slot]);
+            } else {
+                const int lp = w0 + (n >> 1);
+                const bool with_k = (lp & 1) == 0 || lp == w0;  // K scale rows: with the first page of a tile this warp reads
+                uint8_t* hdr = R.hdr[(n >> 1) % kHdrs];
+                mbar_expect_tx(&R.bars[slot], kChunkBytes + kHdrV + (with_k ? kHdrK : 0));
+                bulk_g2s(dst, kc + static_cast<size_t>(pid) * code_stride, kChunkBytes, &R.bars[slot]);
+                bulk_g2s(hdr, vsr + static_cast<size_t>(pid) * (static_cast<uint32_t>(L.kv_heads) * kHdrV), kHdrV, &R.bars[slot]);
+                if (with_k) bulk_g2s(hdr + kHdrV, ksr + static_cast<size_t>(pid) * (static_cast<uint32_t>(L.kv_heads) * kHdrK), kHdrK, &R.bars[slot]);
+            }
+        }
+    };
+    if (nchunks > 0) issue_next(0);
 
     // ---- q' = H q * scale * log2(e) for the rows of this block, stored in fragment order
 #pragma unroll
-    for (int i = 0; i < NB; ++i) {
-        if (warp < 8) {
-            const int r = warp + 8 * i;
+    for (int i = 0; i < kQIter; ++i) {
+        const int r = warp + W * i;
+        if (r < 8 * NB) {
             float v[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) v[j] = L.dtype == KVB_DTYPE_BF16 ? in_to_f32<true>(qraw[i][j]) : in_to_f32<false>(qraw[i][j]);
@@ -434,7 +448,7 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
             }
         }
     }
-    for (; n_issued < kSlots && n_issued < nchunks; ++n_issued) issue_chunk(n_issued, n_issued);
+    while (n_issued < kSlots && n_issued < nchunks) issue_next(n_issued);
     launch_dependents();  // the reduce kernel may take its place on the SMs; it waits for this grid's completion
     __syncthreads();
 
@@ -462,264 +476,251 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
         acc.l[nb][0] = acc.l[nb][1] = acc.z[nb][0] = acc.z[nb][1] = 0.0f;
     }
 
-    // ---- open tile (last split of the head): warp w < 8 takes keys 16w .. 16w+15 of the tile, un-quantised, from
-    //      the stage; its loads are in flight together with the first chunks of the ring
-    if (split == P.nsplit - 1 && warp < 8) {
+    // ---- open tile (last split of the head): its eight 16-key groups are dealt to the consumer warps, un-quantised,
+    //      from the stage; the loads are in flight together with the first chunks of the ring
+    if (split == P.nsplit - 1) {
         const int tile = kv_total / kTile, base = tile * kTile;
-        const int first = base + 16 * warp;
-        if (first < key_end && first + 16 > key_begin && first < kv_total) {
-            QFrag<NB> qf;
-            build_qfrag<NB>(sm, lane, qf);
-            process_stage_group<NB>(L.stage_row(0, tile & 1, head, 16 * warp), L.stage_row(1, tile & 1, head, 16 * warp), qf,
-                                    acc, lane, first, kv_total, row_lim, key_begin, key_end);
+        for (int grp = warp; grp < 8; grp += W) {
+            const int first = base + 16 * grp;
+            if (first < key_end && first + 16 > key_begin && first < kv_total) {
+                QFrag<NB> qf;
+                build_qfrag<NB>(sm, lane, qf);
+                process_stage_group<NB>(L.stage_row(0, tile & 1, head, 16 * grp), L.stage_row(1, tile & 1, head, 16 * grp), qf,
+                                        acc, lane, first, kv_total, row_lim, key_begin, key_end);
+            }
         }
     }
 
-    // ---- sealed tiles
+    // ---- sealed pages
     bool timed_out = false;
-    int n_done = 0;            // chunks consumed
-    int slot = 0;              // slot of chunk n_done
-    uint32_t phases = 0;       // bit s: parity the next wait on slot s expects; bits 8, 9: the header barriers
-    auto wait_chunk = [&]() -> const uint8_t* {
-        if (!((bad_chunks >> slot) & 1u) && !timed_out && !mbar_wait_bounded(&R.bars[slot], (phases >> slot) & 1u)) timed_out = true;
-        return R.slots[slot];
+    int slot = 0;          // slot of the oldest chunk not yet released
+    uint32_t phases = 0;   // bit s: parity the next wait on slot s expects
+    // Wait for the chunk in slot s (bounded).  The first probe usually succeeds; a lane that has to keep probing finds
+    // the barrier complete as soon as any lane has, so the verdict is the same in every lane without a vote.
+    auto wait_slot = [&](int s) {
+        if (timed_out) return;
+        if (!mbar_try_wait(&R.bars[s], (phases >> s) & 1u) && !mbar_wait_lane_bounded(&R.bars[s], (phases >> s) & 1u)) timed_out = true;
     };
-    auto release_chunk = [&]() {  // the chunk in `slot` has been read by every lane: refill the slot, advance
-        const bool was_bad = (bad_chunks >> slot) & 1u;
-        if (!was_bad) phases ^= 1u << slot;
+    auto release_chunk = [&](bool was_live) {  // the chunk in `slot` has been read by every lane: refill the slot, advance
+        if (was_live) phases ^= 1u << slot;
+        live &= ~(1u << slot);
         __syncwarp();
-        if (n_issued < nchunks && !timed_out) {
+        if (n_issued < nchunks) {
             if (lane == 0) fence_proxy_async();  // generic-proxy reads of the slot are ordered before the refill
-            issue_chunk(n_issued, slot);
-            ++n_issued;
-        } else {
-            bad_chunks |= 1u << slot;  // nothing in flight here any more
+            issue_next(slot);
         }
-        ++n_done;
         slot = slot + 1 == kSlots ? 0 : slot + 1;
     };
+    // Key order inside a page: m-row i of 16-key group grp (lane g holds rows g and g + 8) is key
+    //   16 ((i & 7) >> 1) + 8 (grp >> 1) + 4 (grp & 1) + 2 (i >> 3) + (i & 1)
+    // so that, after the accumulator -> operand transposition, the weights of a group line up with the keys ldmatrix
+    // gathers from the four shifted sub-blocks of the V chunk.
+    const int key_lo = 16 * (g >> 1) + (g & 1);  // + 8 (grp >> 1) + 4 (grp & 1): key of m-row g; m-row g + 8 is 2 keys further
 
-    for (int ti = 0; ti < ntiles; ++ti) {
-        const int hb = ti & 1;
-        {   // page ids: keep the window [ids_base, ids_base + 64) ahead of every lookup of this tile and its prefetches
-            if (2 * (w0 + ti) - ids_base >= 32) {
-                ids = ids_next;
-                ids_base += 32;
-                ids_next = load_ids(ids_base + 32);
-            }
+    QInt<NB> qi;
+    int cur_tile = -1;
+    for (int pi = 0; pi < npages; ++pi) {
+        const int lp = w0 + pi;
+        timed_out = __any_sync(0xffffffffu, timed_out);  // one verdict for the warp before anything branches on it
+        if (timed_out) break;
+        if (!((live >> slot) & 1u)) {  // a page that could not be addressed: nothing was copied, nothing is read
+            release_chunk(false);
+            release_chunk(false);
+            continue;
         }
-        if (ti + 1 < ntiles && !timed_out) {  // the other header buffer was last read during tile ti - 1
+        // ---- K chunk + header
+        wait_slot(slot);
+        const uint8_t* hdr = R.hdr[pi % kHdrs];
+        if ((lp >> 1) != cur_tile) {  // per-dim scale / zero point of K belong to the tile
+            cur_tile = lp >> 1;
             __syncwarp();
-            if (lane == 0) fence_proxy_async();
-            issue_header(ti + 1);
+            transpose_k_scale(hdr + kHdrV, R, lane);
+            __syncwarp();
+            build_qint<NB>(sm, R, lane, qi);
         }
-        const bool hdr_ok = !((bad_hdr >> hb) & 1u);
-        if (hdr_ok && !timed_out && !mbar_wait_bounded(&R.hbars[hb], (phases >> (8 + hb)) & 1u)) timed_out = true;
-        if (hdr_ok) phases ^= 1u << (8 + hb);
-        const uint8_t* hdr = R.hdr[hb];
-        QInt<NB> qi;
-        __syncwarp();
-        transpose_k_scale(hdr, R.scratch, lane);
-        __syncwarp();
-        build_qint<NB>(sm, R.scratch, lane, qi);
-
+        const int first = lp * kPage;
+        const bool need_mask = first + kPage - 1 > min_lim || first < key_begin || first + kPage > key_end;
+        // ---- QK: integer logits of the page
+        int tot[NB][kGroups][4];
+        {
+            const uint8_t* ch = R.slots[slot] + key_lo * 64 + 16 * t;
 #pragma unroll
-        for (int pass = 0; pass < kPasses; ++pass) {
-            const int first = (w0 + ti) * kTile + pass * kPassKeys;
-            const bool need_mask = first + kPassKeys - 1 > min_lim || first < key_begin || first + kPassKeys > key_end;
-            // ---- QK: integer logits of the pass
-            int tot[NB][kPassGroups][4];
-            uint64_t dead = 0;  // bit 4 grp + e (+ 32 nb): a key this row may not see (mask, range, or a page that could not be read)
-            bool any_dead = need_mask;
+            for (int grp = 0; grp < kGroups; ++grp) {
+                const int koff = (8 * (grp >> 1) + 4 * (grp & 1)) * 64;
+                const uint4 ka = *reinterpret_cast<const uint4*>(ch + koff);
+                const uint4 kb8 = *reinterpret_cast<const uint4*>(ch + koff + 2 * 64);
+                const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb8.x, kb8.y, kb8.z, kb8.w};
+                int ceh[NB][4], cel[NB][4], coh[NB][4], col[NB][4];
 #pragma unroll
-            for (int c = 0; c < kPassChunks; ++c) {
-                const bool skip = (bad_chunks >> slot) & 1u;
-                const uint8_t* ch = wait_chunk();
+                for (int kb = 0; kb < 2; ++kb) {
+                    const uint32_t l0 = wa[2 * kb] & 0x0F0F0F0Fu, l1 = wb[2 * kb] & 0x0F0F0F0Fu, l2 = wa[2 * kb + 1] & 0x0F0F0F0Fu,
+                                   l3 = wb[2 * kb + 1] & 0x0F0F0F0Fu;
+                    const uint32_t h0 = wa[2 * kb] & 0xF0F0F0F0u, h1 = wb[2 * kb] & 0xF0F0F0F0u, h2 = wa[2 * kb + 1] & 0xF0F0F0F0u,
+                                   h3 = wb[2 * kb + 1] & 0xF0F0F0F0u;
 #pragma unroll
-                for (int gc = 0; gc < 2; ++gc) {
-                    const int grp = 2 * c + gc;
-                    const uint4 ka = *reinterpret_cast<const uint4*>(ch + (gc * 16 + g) * 64 + 16 * t);
-                    const uint4 kb8 = *reinterpret_cast<const uint4*>(ch + (gc * 16 + 8 + g) * 64 + 16 * t);
-                    const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb8.x, kb8.y, kb8.z, kb8.w};
-                    int ceh[NB][4], cel[NB][4], coh[NB][4], col[NB][4];
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) ceh[nb][e] = cel[nb][e] = coh[nb][e] = col[nb][e] = 0;
-#pragma unroll
-                    for (int kb = 0; kb < 2; ++kb) {
-                        const uint32_t l0 = wa[2 * kb] & 0x0F0F0F0Fu, l1 = wb[2 * kb] & 0x0F0F0F0Fu, l2 = wa[2 * kb + 1] & 0x0F0F0F0Fu,
-                                       l3 = wb[2 * kb + 1] & 0x0F0F0F0Fu;
-                        const uint32_t h0 = wa[2 * kb] & 0xF0F0F0F0u, h1 = wb[2 * kb] & 0xF0F0F0F0u, h2 = wa[2 * kb + 1] & 0xF0F0F0F0u,
-                                       h3 = wb[2 * kb + 1] & 0xF0F0F0F0u;
-#pragma unroll
-                        for (int nb = 0; nb < NB; ++nb) {
+                    for (int nb = 0; nb < NB; ++nb) {
+                        if (kb == 0) {
+                            imma_us0(ceh[nb], l0, l1, l2, l3, qi.b[nb][kb][0][0][0], qi.b[nb][kb][0][0][1]);
+                            imma_uu0(cel[nb], l0, l1, l2, l3, qi.b[nb][kb][0][1][0], qi.b[nb][kb][0][1][1]);
+                            imma_us0(coh[nb], h0, h1, h2, h3, qi.b[nb][kb][1][0][0], qi.b[nb][kb][1][0][1]);
+                            imma_uu0(col[nb], h0, h1, h2, h3, qi.b[nb][kb][1][1][0], qi.b[nb][kb][1][1][1]);
+                        } else {
                             imma_us(ceh[nb], l0, l1, l2, l3, qi.b[nb][kb][0][0][0], qi.b[nb][kb][0][0][1]);
                             imma_uu(cel[nb], l0, l1, l2, l3, qi.b[nb][kb][0][1][0], qi.b[nb][kb][0][1][1]);
                             imma_us(coh[nb], h0, h1, h2, h3, qi.b[nb][kb][1][0][0], qi.b[nb][kb][1][0][1]);
                             imma_uu(col[nb], h0, h1, h2, h3, qi.b[nb][kb][1][1][0], qi.b[nb][kb][1][1][1]);
                         }
                     }
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)  // 16 * sum = 256 (16 even_hi + odd_hi) + (16 even_lo + odd_lo); |.| < 2^31
-                            tot[nb][grp][e] = ((ceh[nb][e] * 16 + coh[nb][e]) << 8) + (cel[nb][e] * 16 + col[nb][e]);
-                    if (skip) {
-                        any_dead = true;
-#pragma unroll
-                        for (int nb = 0; nb < NB; ++nb) dead |= 0xFull << (32 * nb + 4 * grp);
-                    }
-                }
-                release_chunk();
-            }
-            if (any_dead) {
-#pragma unroll
-                for (int grp = 0; grp < kPassGroups; ++grp)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int p = first + grp * 16 + g + (e >> 1) * 8;
-                        const bool out = p < key_begin || p >= key_end;
-#pragma unroll
-                        for (int nb = 0; nb < NB; ++nb) {
-                            if (out || p > row_lim[nb][e & 1]) dead |= 1ull << (32 * nb + 4 * grp + e);
-                            if ((dead >> (32 * nb + 4 * grp + e)) & 1ull) tot[nb][grp][e] = INT_MIN;
-                        }
-                    }
-            }
-            // ---- softmax of the pass relative to its own row maxima; weights of the pass against the running state
-            float wq[NB][2];     // weight of the integer sums of this pass in the running accumulators
-            float pf[NB][kPassGroups][4];
-            {
-                // per-key scale of V: the largest of the pass bounds p * scale_V; one factor for all rows
-                const uint8_t* vsc = hdr + kHdrK + (kPasses == 1 ? 0 : pass * kHdrV);
-                float svmax = 0.0f;
-#pragma unroll
-                for (int i = 0; i < kPassKeys / 32; ++i)
-                    svmax = fmaxf(svmax, fabsf(__half2float(*reinterpret_cast<const __half*>(vsc + (lane + 32 * i) * 8 + 4))));
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) svmax = fmaxf(svmax, __shfl_xor_sync(0xffffffffu, svmax, o));
-                const float F = svmax > 0.0f ? kPMax / svmax : 0.0f, invF = svmax * (1.0f / kPMax);
-                float alpha[NB][2], wpass[NB][2], cst[NB][2];
-                bool moved = false;
-#pragma unroll
-                for (int nb = 0; nb < NB; ++nb) {
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        int mx = INT_MIN;
-#pragma unroll
-                        for (int grp = 0; grp < kPassGroups; ++grp) mx = max(mx, max(tot[nb][grp][j], tot[nb][grp][2 + j]));
-                        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-                        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-                        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-                        const float mpass = mx == INT_MIN ? -INFINITY : fmaf(static_cast<float>(mx), qi.f[nb][j], qi.qz[nb][j]);
-                        const float mnew = fmaxf(acc.m[nb][j], mpass);
-                        moved |= mnew > acc.m[nb][j];
-                        const float muse = mnew == -INFINITY ? 0.0f : mnew;
-                        alpha[nb][j] = fast_exp2(acc.m[nb][j] - muse);
-                        wpass[nb][j] = fast_exp2(mpass - muse);
-                        cst[nb][j] = qi.qz[nb][j] - (mpass == -INFINITY ? 0.0f : mpass);
-                        acc.m[nb][j] = mnew;
-                        wq[nb][j] = wpass[nb][j] * invF;
-                    }
-                }
-                if (__any_sync(0xffffffffu, moved)) rescale<NB>(acc, alpha);
-                float lp[NB][2], zp[NB][2];
-#pragma unroll
-                for (int nb = 0; nb < NB; ++nb) lp[nb][0] = lp[nb][1] = zp[nb][0] = zp[nb][1] = 0.0f;
-#pragma unroll
-                for (int grp = 0; grp < kPassGroups; ++grp) {
-                    // V scale rows are [other other scale zp] per key; the pages of the pass are contiguous in the header
-                    const float2 sz0 = unpack_half2(*reinterpret_cast<const uint32_t*>(vsc + (grp * 16 + g) * 8 + 4));      // (scale, zp) of key g
-                    const float2 sz1 = unpack_half2(*reinterpret_cast<const uint32_t*>(vsc + (grp * 16 + 8 + g) * 8 + 4));  // ... of key g + 8
-                    const float sf0 = sz0.x * F, sf1 = sz1.x * F;
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb) {
-                        float p[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            p[e] = fast_exp2(fmaf(static_cast<float>(tot[nb][grp][e]), qi.f[nb][e & 1], cst[nb][e & 1]));
-                            if (any_dead && ((dead >> (32 * nb + 4 * grp + e)) & 1ull)) p[e] = 0.0f;
-                            lp[nb][e & 1] += p[e];
-                        }
-                        zp[nb][0] += p[0] * sz0.y + p[2] * sz1.y;
-                        zp[nb][1] += p[1] * sz0.y + p[3] * sz1.y;
-                        pf[nb][grp][0] = fmaf(p[0], sf0, kMagic); pf[nb][grp][1] = fmaf(p[1], sf0, kMagic);
-                        pf[nb][grp][2] = fmaf(p[2], sf1, kMagic); pf[nb][grp][3] = fmaf(p[3], sf1, kMagic);
-                    }
                 }
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        acc.l[nb][j] = fmaf(lp[nb][j], wpass[nb][j], acc.l[nb][j]);
-                        acc.z[nb][j] = fmaf(zp[nb][j], wpass[nb][j], acc.z[nb][j]);
-                    }
+                    for (int e = 0; e < 4; ++e)  // 16 * sum = 256 (16 even_hi + odd_hi) + (16 even_lo + odd_lo); |.| < 2^31
+                        tot[nb][grp][e] = ((ceh[nb][e] * 16 + coh[nb][e]) << 8) + (cel[nb][e] * 16 + col[nb][e]);
             }
-            // ---- 16-bit weights -> B fragments: accumulator layout (key g; rows 2t, 2t+1) -> operand layout (row g; keys)
-            uint32_t bh[NB][kPassGroups], bl[NB][kPassGroups];
+        }
+        release_chunk(true);
+        if (need_mask) {  // keys a row may not see (causal limit, key range) leave the row maximum ...
+#pragma unroll
+            for (int grp = 0; grp < kGroups; ++grp)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int p = first + key_lo + 8 * (grp >> 1) + 4 * (grp & 1) + 2 * (e >> 1);
+                    const bool out = p < key_begin || p >= key_end;
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb)
+                        if (out || p > row_lim[nb][e & 1]) tot[nb][grp][e] = INT_MIN;
+                }
+        }
+        // ---- softmax of the page relative to its own row maxima; weights of the page against the running state
+        float wq[NB][2];     // weight of the integer sums of this page in the running accumulators
+        uint32_t bh[NB][kGroups], bl[NB][kGroups];  // 16-bit weights as B fragments: high and low bytes
+        {
+            // per-key scale of V: the largest of the page bounds p * scale_V; one factor for all rows
+            float svmax = fmaxf(fabsf(__half2float(*reinterpret_cast<const __half*>(hdr + lane * 8 + 4))),
+                                fabsf(__half2float(*reinterpret_cast<const __half*>(hdr + (lane + 32) * 8 + 4))));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) svmax = fmaxf(svmax, __shfl_xor_sync(0xffffffffu, svmax, o));
+            const float F = svmax > 0.0f ? kPMax / svmax : 0.0f, invF = svmax * (1.0f / kPMax);
+            float alpha[NB][2], wpass[NB][2], cst[NB][2];
+            bool moved = false;
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    int mx = INT_MIN;
+#pragma unroll
+                    for (int grp = 0; grp < kGroups; ++grp) mx = max(mx, max(tot[nb][grp][j], tot[nb][grp][2 + j]));
+                    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                    const float mpass = mx == INT_MIN ? -INFINITY : fmaf(static_cast<float>(mx), qi.f[nb][j], qi.qz[nb][j]);
+                    const float mnew = fmaxf(acc.m[nb][j], mpass);
+                    moved |= mnew > acc.m[nb][j];
+                    const float muse = mnew == -INFINITY ? 0.0f : mnew;
+                    alpha[nb][j] = fast_exp2(acc.m[nb][j] - muse);
+                    wpass[nb][j] = fast_exp2(mpass - muse);
+                    cst[nb][j] = qi.qz[nb][j] - (mpass == -INFINITY ? 0.0f : mpass);
+                    acc.m[nb][j] = mnew;
+                    wq[nb][j] = wpass[nb][j] * invF;
+                }
+            }
+            if (__any_sync(0xffffffffu, moved)) rescale<NB>(acc, alpha);
+            float sl[NB][kGroups][4];  // logits relative to the page maximum (log2 units)
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-                for (int grp = 0; grp < kPassGroups; ++grp) {
-                    const uint32_t y0 = movmatrix_trans(prmt(__float_as_uint(pf[nb][grp][0]), __float_as_uint(pf[nb][grp][1]), 0x5410));  // keys 2t, 2t+1
-                    const uint32_t y1 = movmatrix_trans(prmt(__float_as_uint(pf[nb][grp][2]), __float_as_uint(pf[nb][grp][3]), 0x5410));  // keys 2t+8, 2t+9
+                for (int grp = 0; grp < kGroups; ++grp)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) sl[nb][grp][e] = fmaf(static_cast<float>(tot[nb][grp][e]), qi.f[nb][e & 1], cst[nb][e & 1]);
+            if (need_mask) {  // ... and get weight exactly zero
+#pragma unroll
+                for (int grp = 0; grp < kGroups; ++grp)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int p = first + key_lo + 8 * (grp >> 1) + 4 * (grp & 1) + 2 * (e >> 1);
+                        const bool out = p < key_begin || p >= key_end;
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb)
+                            if (out || p > row_lim[nb][e & 1]) sl[nb][grp][e] = -INFINITY;
+                    }
+            }
+            float lp_[NB][2], zp_[NB][2];
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) lp_[nb][0] = lp_[nb][1] = zp_[nb][0] = zp_[nb][1] = 0.0f;
+            const uint8_t* vs = hdr + key_lo * 8 + 4;  // V scale rows are [other other scale zp] per key
+#pragma unroll
+            for (int grp = 0; grp < kGroups; ++grp) {
+                const int koff = (8 * (grp >> 1) + 4 * (grp & 1)) * 8;
+                const float2 sz0 = unpack_half2(*reinterpret_cast<const uint32_t*>(vs + koff));           // (scale, zp) of the key of m-row g
+                const float2 sz1 = unpack_half2(*reinterpret_cast<const uint32_t*>(vs + koff + 2 * 8));   // ... of m-row g + 8
+                const float sf0 = sz0.x * F, sf1 = sz1.x * F;
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) {
+                    float p[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        p[e] = fast_exp2(sl[nb][grp][e]);
+                        lp_[nb][e & 1] += p[e];
+                    }
+                    zp_[nb][0] += p[0] * sz0.y + p[2] * sz1.y;
+                    zp_[nb][1] += p[1] * sz0.y + p[3] * sz1.y;
+                    // accumulator layout (m-row g; rows 2t, 2t+1) -> operand layout (row g; m-rows 2t, 2t+1 | 2t+8, 2t+9)
+                    const uint32_t y0 = movmatrix_trans(prmt(__float_as_uint(fmaf(p[0], sf0, kMagic)), __float_as_uint(fmaf(p[1], sf0, kMagic)), 0x5410));
+                    const uint32_t y1 = movmatrix_trans(prmt(__float_as_uint(fmaf(p[2], sf1, kMagic)), __float_as_uint(fmaf(p[3], sf1, kMagic)), 0x5410));
                     bl[nb][grp] = prmt(y0, y1, 0x6420);
                     bh[nb][grp] = prmt(y0, y1, 0x7531);
                 }
-            // ---- PV on the int8 path.  ldmatrix.trans hands lane (g, t) the code bytes of dims 32 db + 4g .. +3 for keys
-            //      2t, 2t+1 (+8, +16, +24) of the chunk; one byte permute gathers four keys of a dim pair, one AND isolates
-            //      the even dim (x) or 16 x the odd dim (y).
-            if constexpr (kDimSweeps > 1) {  // the V chunks of the pass stay in their slots for every sweep: wait for all first
-                int s2 = slot;
-#pragma unroll
-                for (int c = 0; c < kPassChunks; ++c) {
-                    if (!((bad_chunks >> s2) & 1u) && !timed_out && !mbar_wait_bounded(&R.bars[s2], (phases >> s2) & 1u)) timed_out = true;
-                    s2 = s2 + 1 == kSlots ? 0 : s2 + 1;
-                }
             }
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    acc.l[nb][j] = fmaf(lp_[nb][j], wpass[nb][j], acc.l[nb][j]);
+                    acc.z[nb][j] = fmaf(zp_[nb][j], wpass[nb][j], acc.z[nb][j]);
+                }
+        }
+        // ---- PV on the int8 path.  Matrix i' of the page (8 rows) gathers keys 2i', 2i'+1 of each of the four sub-blocks:
+        //      eight distinct 16-byte bank groups.  ldmatrix.trans hands lane (g, t) the code bytes of dims 32 db + 4g .. +3
+        //      of keys 16t + 2i', +1; one byte permute gathers keys 16t + 8c + {0..3} (then + {4..7}) of a dim pair, one AND
+        //      isolates the even dim (x) or 16 x the odd dim (y): the k slots of MMA c, matching groups 2c and 2c + 1.
+        wait_slot(slot);
+        {
+            // lane L addresses row L & 7 of matrix L >> 3: key 16 ((L & 7) >> 1) + 2 (L >> 3) + (L & 1) (+ 8c), shifted with its sub-block
+            const int vkey = 16 * ((lane & 7) >> 1) + 2 * (lane >> 3) + (lane & 1);
+            const uint8_t* ch = R.slots[slot] + vkey * 64 + 16 * (vkey >> 4);
 #pragma unroll
             for (int sweep = 0; sweep < kDimSweeps; ++sweep) {
                 constexpr int kDb = 4 / kDimSweeps;
                 int ix[NB][kDb][2][2][4];  // [nb][db][xy][digit][c]
 #pragma unroll
-                for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                    for (int d = 0; d < kDb; ++d)
-#pragma unroll
-                        for (int a = 0; a < 4; ++a)
-#pragma unroll
-                            for (int c = 0; c < 4; ++c) ix[nb][d][a >> 1][a & 1][c] = 0;
-                int vslot = slot;  // sweeps before the last walk the slots without releasing them
-#pragma unroll
-                for (int c = 0; c < kPassChunks; ++c) {
-                    const bool last = sweep == kDimSweeps - 1;
-                    const int cs = last ? slot : vslot;
-                    const bool skip = (bad_chunks >> cs) & 1u;
-                    const uint8_t* ch = (kDimSweeps == 1) ? wait_chunk() : R.slots[cs];
+                for (int c = 0; c < 2; ++c) {  // 32-key halves of the page: keys 16t + 8c + {0..7}
 #pragma unroll
                     for (int d = 0; d < kDb; ++d) {
                         const int db = sweep * kDb + d;
                         uint32_t r[4];
-                        ldsm_x4_trans(r, ch + lane * 64 + 16 * db);
+                        ldsm_x4_trans(r, ch + c * 8 * 64 + 16 * db);
                         const uint32_t u0 = prmt(r[0], r[1], 0x6420), v0 = prmt(r[0], r[1], 0x7531);
                         const uint32_t u1 = prmt(r[2], r[3], 0x6420), v1 = prmt(r[2], r[3], 0x7531);
                         const uint32_t ax0 = u0 & 0x0F0F0F0Fu, ax1 = v0 & 0x0F0F0F0Fu, ax2 = u1 & 0x0F0F0F0Fu, ax3 = v1 & 0x0F0F0F0Fu;
                         const uint32_t ay0 = u0 & 0xF0F0F0F0u, ay1 = v0 & 0xF0F0F0F0u, ay2 = u1 & 0xF0F0F0F0u, ay3 = v1 & 0xF0F0F0F0u;
-                        if (!skip) {
 #pragma unroll
-                            for (int nb = 0; nb < NB; ++nb) {
-                                imma_uu(ix[nb][d][0][0], ax0, ax1, ax2, ax3, bh[nb][2 * c], bh[nb][2 * c + 1]);
-                                imma_uu(ix[nb][d][0][1], ax0, ax1, ax2, ax3, bl[nb][2 * c], bl[nb][2 * c + 1]);
-                                imma_uu(ix[nb][d][1][0], ay0, ay1, ay2, ay3, bh[nb][2 * c], bh[nb][2 * c + 1]);
-                                imma_uu(ix[nb][d][1][1], ay0, ay1, ay2, ay3, bl[nb][2 * c], bl[nb][2 * c + 1]);
+                        for (int nb = 0; nb < NB; ++nb) {
+                            if (c == 0) {
+                                imma_uu0(ix[nb][d][0][0], ax0, ax1, ax2, ax3, bh[nb][0], bh[nb][1]);
+                                imma_uu0(ix[nb][d][0][1], ax0, ax1, ax2, ax3, bl[nb][0], bl[nb][1]);
+                                imma_uu0(ix[nb][d][1][0], ay0, ay1, ay2, ay3, bh[nb][0], bh[nb][1]);
+                                imma_uu0(ix[nb][d][1][1], ay0, ay1, ay2, ay3, bl[nb][0], bl[nb][1]);
+                            } else {
+                                imma_uu(ix[nb][d][0][0], ax0, ax1, ax2, ax3, bh[nb][2], bh[nb][3]);
+                                imma_uu(ix[nb][d][0][1], ax0, ax1, ax2, ax3, bl[nb][2], bl[nb][3]);
+                                imma_uu(ix[nb][d][1][0], ay0, ay1, ay2, ay3, bh[nb][2], bh[nb][3]);
+                                imma_uu(ix[nb][d][1][1], ay0, ay1, ay2, ay3, bl[nb][2], bl[nb][3]);
                             }
                         }
                     }
-                    if (last) release_chunk();
-                    else vslot = vslot + 1 == kSlots ? 0 : vslot + 1;
                 }
-                // ---- integer sums of the pass -> running fp32 accumulators
+                // ---- integer sums of the page -> running fp32 accumulators
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
@@ -729,23 +730,22 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
 #pragma unroll
                             for (int c = 0; c < 4; ++c) {
                                 const float v = static_cast<float>((ix[nb][d][xy][0][c] << 8) + ix[nb][d][xy][1][c]);
-                                acc.o[nb][sweep * kDb + d][xy][c] = fmaf(v, wq[nb][c & 1] * (xy ? 0.0625f : 1.0f), acc.o[nb][sweep * kDb + d][xy][c]);
+                                acc.o[nb][sweep * kDb + d][xy][c] = fmaf(v, xy ? wq[nb][c & 1] * 0.0625f : wq[nb][c & 1], acc.o[nb][sweep * kDb + d][xy][c]);
                             }
             }
         }
+        release_chunk(true);
     }
-    if (timed_out) {
+    if (__any_sync(0xffffffffu, timed_out)) {
         if (lane == 0) L.flag(KVB_ERR_WAIT_TIMEOUT);
         // copies already issued must land before the CTA's shared memory is released: one more bounded wait each
-        for (int s = 0; s < kSlots; ++s)
-            if (!((bad_chunks >> s) & 1u)) mbar_wait_bounded(&R.bars[s], (phases >> s) & 1u);
-        for (int h = 0; h < 2; ++h) mbar_wait_bounded(&R.hbars[h], (phases >> (8 + h)) & 1u);
+        for (int s2 = 0; s2 < kSlots; ++s2)
+            if ((live >> s2) & 1u) mbar_wait_lane_bounded(&R.bars[s2], (phases >> s2) & 1u);
     }
 
-    // ---- merge the warps of the CTA (log-sum-exp) and store one partial per row
-    __syncthreads();  // every slot has been consumed: the ring memory becomes the merge buffer
-    constexpr int kORow = D + 4, kWarpFloats = 3 * kRows + kRows * kORow;
-    static_assert(kWarps * kWarpFloats * 4 <= static_cast<int>(sizeof(WarpRing)) * kWarps, "merge buffer exceeds the rings");
+    // ---- merge the warps of the CTA (log-sum-exp) and store one partial per row; every slot has been consumed: the
+    //      ring memory becomes the merge buffer
+    __syncthreads();
     float* mbuf = reinterpret_cast<float*>(sm.ring) + warp * kWarpFloats;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {

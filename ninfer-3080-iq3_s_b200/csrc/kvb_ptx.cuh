@@ -44,6 +44,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return __all_sync(0xffffffffu, ok);
 }
 
+// The same wait for lanes that may have diverged (some found the barrier complete at their first probe): no vote.
+// Every lane probes the same barrier phase, so a lane can run out of probes only if no lane ever saw it complete.
+__device__ __forceinline__ bool mbar_wait_lane_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
 // Generic-proxy accesses to shared memory made before this fence are ordered before later async-proxy
 // (bulk copy) accesses: needed before a buffer that was read with ld.shared is refilled by a bulk copy.
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

@@ -8,7 +8,8 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 GOLDEN = os.path.join(ROOT, "tests", "golden")
-REFERENCE_ROOT = os.environ.get("KVB_REFERENCE_ROOT", "/root/reference")
+# a checkout of the reference, if any: KVB_REFERENCE_ROOT, else a directory named "reference" beside this repository
+REFERENCE_ROOT = os.environ.get("KVB_REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
 
 
 def pytest_configure(config):

@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Regenerates the golden fixtures in this directory from the reference repository.
 
-Run in a container where the reference is mounted:  python tests/golden/make_golden.py [REFERENCE_ROOT]
+Run where a checkout of the reference is available:  python tests/golden/make_golden.py REFERENCE_ROOT
 
 Fixtures written (all derived from data files of the reference, no source code):
   gvk2_it0.npz    8 of the 32 GVK2 records of kvarn-evidence/verify-g128/data/real_k4v4_it0.bin
@@ -47,7 +47,9 @@ def read_gvk2(path):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("KVB_REFERENCE_ROOT", "")
+    if not os.path.isdir(os.path.join(root, "kvarn-evidence")):
+        sys.exit("reference sources absent: pass the reference checkout as the first argument or set KVB_REFERENCE_ROOT")
     ev = os.path.join(root, "kvarn-evidence")
     it0 = read_gvk2(os.path.join(ev, "verify-g128/data/real_k4v4_it0.bin"))
     pick = [r for r in it0 if r["name"] in (

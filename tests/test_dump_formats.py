@@ -113,7 +113,9 @@ def test_reference_verifier_accepts_planes_written_by_the_gpu(tmp_path, iters):
 # --------------------------------------------------------------------------------------------------------------
 # GVK2: the record dump of the reference's byte-for-byte quantiser gate.
 GOLDEN = os.path.join(ROOT, "tests", "golden")
-REF_GVK2 = os.path.join(os.environ.get("KVB_REFERENCE_ROOT", ""), "kvarn-evidence", "verify-g128", "data", "real_k4v4_it0.bin")
+from conftest import REFERENCE_ROOT  # noqa: E402
+
+REF_GVK2 = os.path.join(REFERENCE_ROOT, "kvarn-evidence", "verify-g128", "data", "real_k4v4_it0.bin")
 
 
 def _stage_from_golden():
