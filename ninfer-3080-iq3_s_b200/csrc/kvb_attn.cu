@@ -27,6 +27,7 @@
 #include <algorithm>
 #include <climits>
 #include <cstddef>
+#include <cstdlib>
 
 #include "kvb_common.cuh"
 #include "kvb_ptx.cuh"
@@ -35,14 +36,14 @@ namespace kvb {
 namespace {
 
 constexpr int D = 128;
-constexpr int kWarpsDecode = 12;    // warps per CTA for up to 8 merged query rows (one N block per warp): 168 registers per thread
+constexpr int kWarpsDecode = 16;    // warps per CTA for up to 8 merged query rows (one N block per warp): 128 registers per thread
 constexpr int kWarpsWide = 8;       // ... for 9..16 merged rows (two N blocks per warp: twice the accumulators): 255 registers
 constexpr int kRows = 16;           // query rows per CTA: one or two 8-row N blocks
 constexpr int kChunkBytes = kPage * (D / 2);  // 4096: the K or the V codes of one page
 constexpr int kVSub = 1024 + 16;    // V codes lie as four sub-blocks of 16 keys, sub-block a at a * kVSub: key k at k * 64 + 16 * (k / 16)
 constexpr int kSlotBytes = 4224;    // 4096 + 48 bytes of sub-block shifts, rounded up to 128
-constexpr int kSlots = 3;           // ring slots per consumer warp
-constexpr int kHdrs = 3;            // header buffers per consumer (a header lives from the issue of its page's K chunk to the end of the page)
+constexpr int kSlots = 2;           // ring slots per warp: the chunk in work and the next one in flight
+constexpr int kHdrs = 2;            // header buffers per warp (a header lives from the issue of its page's K chunk to the end of the page)
 constexpr int kHdrV = 512, kHdrK = 640, kHdrBytes = kHdrV + kHdrK;  // V scale rows of the page, then (first page of a tile) the K scale rows
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kMagic = 12582912.0f;   // 1.5 * 2^23: x + kMagic has round(x) in its low mantissa bits (|x| < 2^22)
@@ -328,7 +329,7 @@ template <int NB, int W>
 __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int head, int zb, int64_t pidx) {
     constexpr int kWarps = W, kThreads = W * 32;
     constexpr int kGroups = kPage / 16;            // 16-key groups of a page
-    constexpr int kDimSweeps = NB;                 // the V chunk of a page is swept once per 128 / NB dims
+    constexpr int kDimSweeps = 2;                  // the V chunk of a page is swept in two halves of the dims: half the integer accumulators at a time
     constexpr int kORow = D + 4, kWarpFloats = 3 * kRows + kRows * kORow;  // merge buffer of a warp: m, l, z per row, then o
     static_assert(kWarps * kWarpFloats * 4 <= static_cast<int>(sizeof(WarpRing)) * kWarps, "merge buffer exceeds the rings");
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -1143,6 +1144,35 @@ int launch_general_attention(const kvb_layer* layer, const void* q, const int32_
                              float* part_l, float* part_o, cudaStream_t stream);
 namespace {
 
+// One attention launch with W warps per CTA (the opt-in to large dynamic shared memory is made once per device and W).
+template <int NB, int W>
+cudaError_t launch_attn(dim3 grid, cudaStream_t stream, const AttnParams& P) {
+    constexpr int smem = static_cast<int>(sizeof(AttnSmem<W>));
+    static unsigned long long opted = 0;
+    if (first_call_on_device(opted)) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_kernel<NB, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+    }
+    return launch_early(attn_kernel<NB, W>, grid, dim3(W * 32), smem, stream, P);
+}
+
+// Warps per CTA for a decode call: 8, 12 or 16 (whole warp quartets: an SM hands registers and issue slots out per
+// quartet, 10 or 14 warps measured no faster per warp than 12 or 16).  A warp works on whole pages and an SM finishes
+// about one page per 0.25 us whatever the number of warps, so a CTA with n pages needs ceil(n / W) rounds of
+// 0.25 W us; set-up and the final merge cost a little more with more warps.  Measured on B200 at 32K .. 379K tokens.
+int decode_warps(int kv_len_max, int nsplit) {
+    static const int forced = [] { const char* e = std::getenv("KVB_DECODE_WARPS"); return e ? std::atoi(e) : 0; }();
+    if (forced == 8 || forced == 12 || forced == 16) return forced;
+    const int pages = 2 * (kv_len_max / kTile), per_cta = (pages + nsplit - 1) / nsplit;
+    int best = 16;
+    float best_cost = 1e30f;
+    for (int w = 16; w >= 8; w -= 4) {
+        const float cost = 5.0f + 0.22f * w + static_cast<float>((per_cta + w - 1) / w) * 0.25f * w;
+        if (cost < best_cost - 1e-3f) { best_cost = cost; best = w; }
+    }
+    return best;
+}
+
 int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_dev, const int32_t* total_pos_dev, int T,
                      float scale, int kv_len_max,
                      int key_begin, int key_end, void* workspace, void* out, float* part_m, float* part_l,
@@ -1176,15 +1206,16 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     P.ws_l = P.ws_m + rows;
     P.ws_o = P.ws_l + rows;
     const bool upper = T * (layer->q_heads / layer->kv_heads) > 8;
-    constexpr int smem1 = static_cast<int>(sizeof(AttnSmem<kWarpsDecode>)), smem2 = static_cast<int>(sizeof(AttnSmem<kWarpsWide>));
-    static unsigned long long opted = 0;
-    if (first_call_on_device(opted)) {
-        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<1, kWarpsDecode>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1));
-        KVB_CUDA_OK(cudaFuncSetAttribute(attn_kernel<2, kWarpsWide>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2));
-    }
     const dim3 grid(parts, layer->kv_heads, Z);
-    if (upper) KVB_CUDA_OK(launch_early(attn_kernel<2, kWarpsWide>, grid, dim3(kWarpsWide * 32), smem2, stream, P));
-    else KVB_CUDA_OK(launch_early(attn_kernel<1, kWarpsDecode>, grid, dim3(kWarpsDecode * 32), smem1, stream, P));
+    if (upper) {
+        KVB_CUDA_OK((launch_attn<2, kWarpsWide>(grid, stream, P)));
+    } else {
+        switch (decode_warps(kv_len_max, nsplit)) {
+            case 8: KVB_CUDA_OK((launch_attn<1, 8>(grid, stream, P))); break;
+            case 12: KVB_CUDA_OK((launch_attn<1, 12>(grid, stream, P))); break;
+            default: KVB_CUDA_OK((launch_attn<1, 16>(grid, stream, P))); break;
+        }
+    }
     const int total_rows = T * layer->q_heads;
     KVB_CUDA_OK(launch_early(reduce_kernel, dim3(total_rows), dim3(kReduceWarps * 32), 0, stream, P.ws_m, P.ws_l, P.ws_o, parts, T,
                              layer->q_heads, layer->kv_heads, Z, layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o,
