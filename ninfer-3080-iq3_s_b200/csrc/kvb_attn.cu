@@ -40,10 +40,17 @@ constexpr int kWarpsDecode = 16;    // warps per CTA for up to 8 merged query ro
 constexpr int kWarpsWide = 8;       // ... for 9..16 merged rows (two N blocks per warp: twice the accumulators): 255 registers
 constexpr int kRows = 16;           // query rows per CTA: one or two 8-row N blocks
 constexpr int kChunkBytes = kPage * (D / 2);  // 4096: the K or the V codes of one page
-constexpr int kVSub = 1024 + 16;    // V codes lie as four sub-blocks of 16 keys, sub-block a at a * kVSub: key k at k * 64 + 16 * (k / 16)
+#ifndef KVB_V_SHIFT
+#define KVB_V_SHIFT 16
+#endif
+constexpr int kVShift = KVB_V_SHIFT;  // 16: V codes lie as four sub-blocks of 16 keys, each shifted 16 bytes further (conflict-free ldmatrix, four copies); 0: one copy
+constexpr int kVSub = 1024 + kVShift;  // sub-block a at a * kVSub: key k at k * 64 + kVShift * (k / 16)
 constexpr int kSlotBytes = 4224;    // 4096 + 48 bytes of sub-block shifts, rounded up to 128
-constexpr int kSlots = 2;           // ring slots per warp: the chunk in work and the next one in flight
-constexpr int kHdrs = 2;            // header buffers per warp (a header lives from the issue of its page's K chunk to the end of the page)
+#ifndef KVB_SLOTS
+#define KVB_SLOTS 2
+#endif
+constexpr int kSlots = KVB_SLOTS;   // ring slots per warp: the chunk in work and the next one(s) in flight
+constexpr int kHdrs = KVB_SLOTS;            // header buffers per warp (a header lives from the issue of its page's K chunk to the end of the page)
 constexpr int kHdrV = 512, kHdrK = 640, kHdrBytes = kHdrV + kHdrK;  // V scale rows of the page, then (first page of a tile) the K scale rows
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kMagic = 12582912.0f;   // 1.5 * 2^23: x + kMagic has round(x) in its low mantissa bits (|x| < 2^22)
@@ -416,8 +423,12 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
             if (n & 1) {
                 const uint8_t* src = vc + static_cast<size_t>(pid) * code_stride;
                 mbar_expect_tx(&R.bars[slot], kChunkBytes);
+                if constexpr (kVShift == 0) {
+                    bulk_g2s(dst, src, kChunkBytes, &R.bars[slot]);
+                } else {
 #pragma unroll
-                for (int a = 0; a < 4; ++a) bulk_g2s(dst + a * kVSub, src + a * 1024, 1024, &R.bars[slot]);
+                    for (int a = 0; a < 4; ++a) bulk_g2s(dst + a * kVSub, src + a * 1024, 1024, &R.bars[slot]);
+                }
             } else {
                 const int lp = w0 + (n >> 1);
                 const bool with_k = (lp & 1) == 0 || lp == w0;  // K scale rows: with the first page of a tile this warp reads
@@ -689,7 +700,7 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
         {
             // lane L addresses row L & 7 of matrix L >> 3: key 16 ((L & 7) >> 1) + 2 (L >> 3) + (L & 1) (+ 8c), shifted with its sub-block
             const int vkey = 16 * ((lane & 7) >> 1) + 2 * (lane >> 3) + (lane & 1);
-            const uint8_t* ch = R.slots[slot] + vkey * 64 + 16 * (vkey >> 4);
+            const uint8_t* ch = R.slots[slot] + vkey * 64 + kVShift * (vkey >> 4);
 #pragma unroll
             for (int sweep = 0; sweep < kDimSweeps; ++sweep) {
                 constexpr int kDb = 4 / kDimSweeps;
@@ -1157,18 +1168,20 @@ cudaError_t launch_attn(dim3 grid, cudaStream_t stream, const AttnParams& P) {
 }
 
 // Warps per CTA for a decode call: 8, 12 or 16 (whole warp quartets: an SM hands registers and issue slots out per
-// quartet, 10 or 14 warps measured no faster per warp than 12 or 16).  A warp works on whole pages and an SM finishes
-// about one page per 0.25 us whatever the number of warps, so a CTA with n pages needs ceil(n / W) rounds of
-// 0.25 W us; set-up and the final merge cost a little more with more warps.  Measured on B200 at 32K .. 379K tokens.
+// quartet; 10 or 14 warps measured no faster per warp than 12 or 16).  A warp works on whole pages, so a CTA with n
+// pages needs ceil(n / W) rounds; a round and the fixed part (set-up, merge of the warps) take longer the more warps
+// share the SM.  Times in microseconds, fitted to sweeps over 32K .. 379K tokens on B200: with 8 warps the SM is
+// not yet saturated (a round of 8 pages takes 2.5 us, one of 16 pages 3.9 us).
 int decode_warps(int kv_len_max, int nsplit) {
     static const int forced = [] { const char* e = std::getenv("KVB_DECODE_WARPS"); return e ? std::atoi(e) : 0; }();
     if (forced == 8 || forced == 12 || forced == 16) return forced;
+    static const struct { int warps; float fixed_us, round_us; } kChoice[3] = {{16, 8.8f, 3.93f}, {12, 7.3f, 2.98f}, {8, 6.1f, 2.52f}};
     const int pages = 2 * (kv_len_max / kTile), per_cta = (pages + nsplit - 1) / nsplit;
     int best = 16;
     float best_cost = 1e30f;
-    for (int w = 16; w >= 8; w -= 4) {
-        const float cost = 5.0f + 0.22f * w + static_cast<float>((per_cta + w - 1) / w) * 0.25f * w;
-        if (cost < best_cost - 1e-3f) { best_cost = cost; best = w; }
+    for (const auto& c : kChoice) {
+        const float cost = c.fixed_us + static_cast<float>((per_cta + c.warps - 1) / c.warps) * c.round_us;
+        if (cost < best_cost - 1e-3f) { best_cost = cost; best = c.warps; }
     }
     return best;
 }
