@@ -312,11 +312,12 @@ def measure_long(E, args, layers_n, with_cpu=True):
         else:
             rdec[i].attn_decode(qkv[i, :QH], p, E.scale, kv_len_max, outs[i])
 
-    def step_body():
+    def step_body():  # per layer: append the new token (owner of the open tile), then decode
         for i, L in enumerate(layers):
             if owner:
-                L.append(qkv[i, QH:QH + H].unsqueeze(0), qkv[i, QH + H:].unsqueeze(0), pos)
-            decode(i, pos if owner else pos_fixed)
+                L.append_decode(qkv[i, :QH], qkv[i, QH:QH + H], qkv[i, QH + H:], pos, E.scale, kv_len_max, out=outs[i], ring=ring)
+            else:
+                decode(i, pos_fixed)
         if owner:
             pos.add_(1)
 
@@ -479,8 +480,7 @@ def measure_decode32k(E, args):
 
     def step_body():
         for i, L in enumerate(layers):
-            L.append(qkv[i, QH:QH + H].unsqueeze(0), qkv[i, QH + H:].unsqueeze(0), pos)
-            L.attn_decode(qkv[i, :QH], pos, E.scale, kv_len_max, out=outs[i])
+            L.append_decode(qkv[i, :QH], qkv[i, QH:QH + H], qkv[i, QH + H:], pos, E.scale, kv_len_max, out=outs[i])
         pos.add_(1)
 
     def decode_only_body():
@@ -688,9 +688,71 @@ def measure_prefill(E, args):
             "bound": "tensor", "clocks": clk.summary(), "error_words": L.errors()}
 
 
+def measure_chunk_sharded(E, args):
+    """The prefill chunk (1,024 tokens over a 262,144-token prefix) or a verify step (8 rows over 131,072 tokens) over a
+    sequence whose tile ranges live on the N ranks: the new rows are appended on the rank that owns the open tile,
+    every rank attends its own range (kvb_attn_chunk_partial), one all-gather of the partials, every rank merges."""
+    torch = E.torch
+    sh = E.pkg.sharded
+    prefill = args.workload == "prefill262k"
+    ctx, tokens = ((args.ctx or 262144), 1024) if prefill else (131072, 8)
+    b, e = sh.tile_ranges(ctx, E.world)[E.rank]
+    n = e - b
+    owner = E.rank == E.world - 1
+    L = E.layer(n, tokens + 8, 100 * E.rank)
+    host_gen = torch.Generator()
+    host_gen.manual_seed(4321)  # the same q and new rows on every rank
+    q = torch.randn((tokens, QH, D), generator=host_gen).to(torch.float16).to(E.dev)
+    kv = torch.randn((tokens, 2 * H, D), generator=host_gen)
+    kv[..., [3, 17, 64, 101]] *= 20.0
+    kv = kv.to(torch.float16).to(E.dev)
+    pos = (torch.arange(n, n + tokens, dtype=torch.int32, device=E.dev) if owner
+           else torch.full((tokens,), n - 1, dtype=torch.int32, device=E.dev))
+    out = torch.empty((tokens, QH, D), dtype=torch.float16, device=E.dev)
+    chunk = sh.ShardedChunk(L, tokens)
+    kv_len_max = n + tokens + 8
+    if tokens > 8:
+        L.prefill_workspace(kv_len_max, tokens)
+    else:
+        L.workspace(kv_len_max, tokens)
+
+    def step():  # the drafts / the chunk are rolled back after every step: the same rows are appended at the same positions
+        chunk.attend(q, kv[:, :H], kv[:, H:], pos, E.scale, kv_len_max, out)
+
+    def step_local():  # without the collective: append + partial only
+        if owner:
+            L.append(kv[:, :H], kv[:, H:], pos)
+        L.attn_chunk_partial_packed(q, pos, E.scale, kv_len_max, chunk.send[:tokens * chunk.per_token])
+
+    step()
+    with ClockSampler(E.local) as clk:
+        for _ in range(max(args.warmup, 3)):
+            step()
+        ms = E.timed(step, args.steps)
+        for _ in range(3):
+            step_local()
+        ms_local = E.timed(step_local, args.steps)
+    peak, peak_tf, kind = peaks()
+    flops = 4.0 * QH * D * (tokens * ctx + tokens * (tokens + 1) / 2)
+    tf = flops / (ms * 1e-3) / 1e12
+    nbytes = decode_bytes(ctx)
+    res = {"workload": (f"prefill chunk of 1,024 tokens over a {ctx}-token prefix" if prefill else "verify step of 8 rows over 131,072 tokens")
+                       + f", tile ranges on {E.world} GPUs: append on the owner, per-rank partials, one all-gather, merge",
+           "us": ms * 1e3, "us_without_collective": ms_local * 1e3, "collective_share": max(0.0, 1.0 - ms_local / ms),
+           "bytes_gathered_per_rank": tokens * QH * (D + 2) * 4, "n_gpus": E.world, "clocks": clk.summary(), "error_words": L.errors()}
+    if prefill:
+        res.update({"achieved": tf, "unit": "TFLOP/s", "frac": tf / (peak_tf * E.world), "peak": peak_tf, "peak_kind": kind + " (sustained bf16, per GPU)", "bound": "tensor"})
+    else:
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        res.update({"achieved": gbs, "unit": "GB/s", "frac": gbs / (peak * E.world), "peak": peak, "peak_kind": kind, "bound": "hbm"})
+    return res
+
+
 def run_single(args, fn, metric, unit):
     """One of the other workloads alone, printed in the contract's line format."""
     E = _Env()
+    if E.world > 1 and args.workload in ("prefill262k", "verify131k"):
+        fn = measure_chunk_sharded
     r = fn(E, args)
     if "metric" not in r:
         r = {"metric": metric, "value": r["achieved"], "unit": unit, "n_gpus": E.world, "steps": args.steps, "warmup": max(args.warmup, 3),

@@ -178,6 +178,14 @@ size_t kvb_peer_ring_bytes(int world, int q_heads, int head_dim);
 int kvb_attn_decode_sharded(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
                             void* workspace, const kvb_peer_ring* ring, void* out, void* stream);
 
+/* One decode step: append the token at *pos_dev (k, v: [kv_heads][head_dim]), then decode attention of q over the
+ * cache including it -- kvb_append followed by kvb_attn_decode (ring == NULL) or kvb_attn_decode_sharded (ring given:
+ * the rank that owns the open tile of a range-sharded sequence), same results bit for bit, one host call instead of
+ * two (an attention kernel that started before the append had finished was measured slower).  The reference's decode
+ * step makes the same pair of calls (kv_cache_append_launch, then causal_attention_cached_small_t_launch, P3:1379, 3612). */
+int kvb_append_decode(const kvb_layer* layer, const void* q, const void* k, const void* v, const int32_t* pos_dev, float scale,
+                      int kv_len_max, void* workspace, const kvb_peer_ring* ring, void* out, void* stream);
+
 /* MTP verify: append `width` (1..8) new rows, then causal attention of those rows (row i sees keys
  * 0..positions[i]).  q, out: [width][q_heads][head_dim]; k, v: [width][kv_heads][head_dim].
  * Replaces causal_attention_small_t_launch (P3:3508-3610). */

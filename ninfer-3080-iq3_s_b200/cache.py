@@ -87,6 +87,17 @@ class KvarnLayer:
                                                _ptr(self.workspace(kv_len_max, 1)), _ptr(out), _stream()))
         return out
 
+    # ---- one decode step: kv_cache_append_launch + causal_attention_cached_small_t_launch as one call
+    def append_decode(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos: torch.Tensor, scale: float, kv_len_max: int,
+                      out=None, ring=None) -> torch.Tensor:
+        """k, v: [1, kv_heads, head_dim] (or [kv_heads, head_dim]); pos: int32 [1] on the device.  `ring`: a
+        sharded.PeerRing when this cache is the last tile range of a range-sharded sequence."""
+        out = torch.empty_like(q) if out is None else out
+        capi.check(capi.load().kvb_append_decode(C.byref(self.c), _ptr(q), _ptr(k), _ptr(v), _ptr(pos), scale, kv_len_max,
+                                                 _ptr(self.workspace(kv_len_max, 1)), None if ring is None else C.byref(ring.c),
+                                                 _ptr(out), _stream()))
+        return out
+
     def attn_decode_partial(self, q, pos, scale, kv_len_max, key_begin=0, key_end=2**31 - 1):
         m = torch.empty(self.q_heads, dtype=torch.float32, device=self.device)
         l = torch.empty_like(m)

@@ -62,6 +62,8 @@ SYMBOLS = {
     "kvb_peer_ring_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "kvb_attn_decode_sharded": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p,
                                           C.POINTER(kvb_peer_ring), C.c_void_p, C.c_void_p]),
+    "kvb_append_decode": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p,
+                                    C.POINTER(kvb_peer_ring), C.c_void_p, C.c_void_p]),
     "kvb_attn_verify": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                   C.c_float, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "kvb_attn_rows": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_float, C.c_int, C.c_void_p,

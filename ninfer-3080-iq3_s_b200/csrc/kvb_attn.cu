@@ -1330,29 +1330,52 @@ extern "C" size_t kvb_peer_ring_bytes(int world, int q_heads, int head_dim) {
     return static_cast<size_t>(2) * world * q_heads * (head_dim + 2) * sizeof(unsigned long long);  // two slots, 8 bytes per value
 }
 
-extern "C" int kvb_attn_decode_sharded(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
-                                       void* workspace, const kvb_peer_ring* ring, void* out, void* stream) {
-    using namespace kvb;
+namespace kvb {
+// Checks a ring descriptor and turns it into the kernel's form.
+static int make_push_target(const kvb_layer* layer, const kvb_peer_ring* ring, const void* out, const char* who, PushTarget& push) {
     if (ring == nullptr || ring->peer_bufs == nullptr || ring->local_buf == nullptr || ring->state == nullptr || out == nullptr)
-        return fail(KVB_EINVAL, "kvb_attn_decode_sharded: null ring / buffers / out");
+        return fail(KVB_EINVAL, "%s: null ring / buffers / out", who);
     if (ring->world < 1 || ring->world > kRingMaxWorld || ring->rank < 0 || ring->rank >= ring->world)
-        return fail(KVB_EINVAL, "kvb_attn_decode_sharded: rank %d of world %d (1..%d ranks)", ring->rank, ring->world, kRingMaxWorld);
-    PushTarget push{};
+        return fail(KVB_EINVAL, "%s: rank %d of world %d (1..%d ranks)", who, ring->rank, ring->world, kRingMaxWorld);
+    push = PushTarget{};
     for (int p = 0; p < ring->world; ++p) {
         if (ring->peer_bufs[p] == nullptr || (reinterpret_cast<uintptr_t>(ring->peer_bufs[p]) & 15u) != 0)
-            return fail(KVB_EINVAL, "kvb_attn_decode_sharded: ring buffer of rank %d is null or not 16-byte aligned", p);
+            return fail(KVB_EINVAL, "%s: ring buffer of rank %d is null or not 16-byte aligned", who, p);
         push.peers[p] = static_cast<unsigned long long*>(ring->peer_bufs[p]);
     }
-    if ((reinterpret_cast<uintptr_t>(ring->local_buf) & 15u) != 0)
-        return fail(KVB_EINVAL, "kvb_attn_decode_sharded: local ring buffer is not 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(ring->local_buf) & 15u) != 0) return fail(KVB_EINVAL, "%s: local ring buffer is not 16-byte aligned", who);
     push.state = ring->state;
     push.local_buf = static_cast<const unsigned long long*>(ring->local_buf);
     push.max_spins = ring->max_spins ? ring->max_spins : (1u << 20);
     push.error_word = layer != nullptr ? layer->error_word : nullptr;
     push.rank = ring->rank;
     push.world = ring->world;
+    return KVB_OK;
+}
+}  // namespace kvb
+
+extern "C" int kvb_attn_decode_sharded(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
+                                       void* workspace, const kvb_peer_ring* ring, void* out, void* stream) {
+    using namespace kvb;
+    PushTarget push{};
+    if (int st = make_push_target(layer, ring, out, "kvb_attn_decode_sharded", push)) return st;
     return launch_attention(layer, q, pos_dev, pos_dev, 1, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr, nullptr,
                             static_cast<cudaStream_t>(stream), "kvb_attn_decode_sharded", &push);
+}
+
+// One decode step of a sequence in one call: append the newest token, then attend (kvb_append followed by
+// kvb_attn_decode, or kvb_attn_decode_sharded when a ring is given, on the same stream).
+extern "C" int kvb_append_decode(const kvb_layer* layer, const void* q, const void* k, const void* v, const int32_t* pos_dev, float scale,
+                                 int kv_len_max, void* workspace, const kvb_peer_ring* ring, void* out, void* stream) {
+    using namespace kvb;
+    if (int st = kvb_append(layer, k, v, pos_dev, 1, stream)) return st;
+    if (ring == nullptr)
+        return launch_attention(layer, q, pos_dev, pos_dev, 1, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr, nullptr,
+                                static_cast<cudaStream_t>(stream), "kvb_append_decode");
+    PushTarget push{};
+    if (int st = make_push_target(layer, ring, out, "kvb_append_decode", push)) return st;
+    return launch_attention(layer, q, pos_dev, pos_dev, 1, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr, nullptr,
+                            static_cast<cudaStream_t>(stream), "kvb_append_decode", &push);
 }
 
 // ---------------------------------------------------------------------------------------------------------

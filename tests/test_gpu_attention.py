@@ -133,6 +133,38 @@ def test_verify_widths_share_one_workspace(H, QH, T):
     assert tw.gpu.errors() == 0
 
 
+@pytest.mark.parametrize("T0", [300, 127, 255, 1000])
+def test_append_decode_equals_append_then_decode(T0):
+    """kvb_append_decode (the attention chained to the append, only the CTAs that read the stage or a freshly sealed tile
+    waiting for it) against kvb_append followed by kvb_attn_decode on a twin cache: same bits, over steps that cross a
+    tile boundary (the append seals a tile in the middle of the run)."""
+    import torch
+
+    H, QH, D, steps = 4, 24, 128, 6
+    k, v = orc.synth_kv(91, T0 + steps, H, D, 1), orc.synth_kv(91, T0 + steps, H, D, 2)
+    q = orc.synth_q(91, steps, QH, D)
+    a = Twin(D=D, H=H, QH=QH, capacity_tokens=T0 + steps, seed=92)
+    b = Twin(D=D, H=H, QH=QH, capacity_tokens=T0 + steps, seed=92)
+    a.append(k[:T0], v[:T0])
+    b.append(k[:T0], v[:T0])
+    scale = 1.0 / np.sqrt(D)
+    for s in range(steps):
+        p = T0 + s
+        pos = torch.tensor([p], dtype=torch.int32, device=a.dev)
+        kd, vd, qd = (torch.from_numpy(x).to(a.dev) for x in (k[p:p + 1], v[p:p + 1], q[s]))
+        got = a.gpu.append_decode(qd, kd, vd, pos, scale, T0 + steps)
+        b.gpu.append(kd, vd, pos)
+        want = b.gpu.attn_decode(qd, pos, scale, T0 + steps)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), (T0, s)
+        a.cpu.append(k[p:p + 1], v[p:p + 1], p)
+        ref = a.cpu.attention(q[s:s + 1], [p], scale, QH, threads=4)[0]
+        ok, msg = attn_close(got.float().cpu().numpy(), ref)
+        assert ok, msg
+    a.len = T0 + steps
+    assert all(a.planes_equal().values()) and a.gpu.errors() == 0
+
+
 def test_partials_merge_to_the_full_answer():
     """Key ranges attended separately and merged by log-sum-exp (what the multi-GPU combine does)."""
     import torch
