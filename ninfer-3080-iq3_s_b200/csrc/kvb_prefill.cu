@@ -4,19 +4,18 @@
 // tile, one KV head and one range of 128-key tiles, and walks its keys flash-attention style:
 //   S = Q K^T   tcgen05.mma, A = Q tile and B = de-quantised K tile in shared memory (K-major, 128-byte swizzle),
 //               accumulator S[128 x 128] fp32 in tensor memory;
-//   softmax     two threads own row r (= TMEM lane r), one per half of the 128 keys (warps w and w + 4 reach the
-//               same lanes): each loads its 64 columns of S with tcgen05.ld, the pair agrees on the row maximum
-//               through shared memory, each keeps the sum of its half, writes its half of P (fp16 pairs) back into
-//               the columns of S, and rescales its half of the O accumulator in TMEM only when a row maximum moved;
+//   softmax     thread r owns row r (= TMEM lane r): loads S with tcgen05.ld, running max / sum in registers,
+//               writes P (fp16) over the K tile (S is complete by then), rescales the O accumulator in TMEM only
+//               when a row maximum moved;
 //   O += P V    tcgen05.mma, A = P tile (K-major over keys), B = de-quantised V tile (MN-major: one 128-byte row
 //               of 64 dims per key), accumulator O[128 x 128] fp32 in tensor memory.
-// K and V tiles are de-quantised by the CUDA cores straight from the planes (thread = half a key row): nibbles -> fp16 with
+// K and V tiles are de-quantised by the CUDA cores straight from the planes (thread = key): nibbles -> fp16 with
 // the exact unpack of the decode kernel, then one fused multiply-add with the tile's per-dim (K) or the key's
 // (V) fp16 scale and zero point.  Dims inside every group of eight are kept in the order the unpack yields
 // (0,4,1,5,2,6,3,7); Q is written in the same order, so the contraction is unaffected, and the merge kernel
 // puts the output dims back.  Keys of the open tile come un-quantised from the stage.
-// Three 32 KB tiles (Q, K, V) and 256 TMEM columns per CTA let two CTAs of eight warps share an SM, so one CTA's
-// CUDA-core phases (de-quantisation, softmax) overlap the other's MMAs and every scheduler has four warps to pick from.
+// Three 32 KB tiles (Q, K/P, V) and 256 TMEM columns per CTA let two CTAs share an SM, so one CTA's CUDA-core
+// phases (de-quantisation, softmax) overlap the other's MMAs.
 // Every wait on an mbarrier is bounded; a wait that gives up sets KVB_ERR_WAIT_TIMEOUT and the CTA leaves
 // through the normal exit (TMEM is freed).
 #include <climits>
@@ -30,7 +29,7 @@ namespace {
 constexpr int D = 128;
 constexpr int kM = 128;        // query rows per CTA
 constexpr int kN = 128;        // keys per step = one quantisation tile
-constexpr int kThreads = 256;  // threads r and r + 128 <-> query row r <-> TMEM lane r, one half of the keys / dims each
+constexpr int kThreads = 128;  // thread r <-> query row r <-> TMEM lane r
 constexpr int kTileBytes = kM * D * 2;
 constexpr uint32_t kTmemCols = 256;  // S at columns [0,128), O at [128,256)
 
@@ -48,14 +47,13 @@ struct PrefillParams {
 
 struct __align__(1024) PrefillSmem {
     uint8_t q[kTileBytes];
-    uint8_t k[kTileBytes];
+    uint8_t k[kTileBytes];  // the K tile, then -- once S = Q K^T has completed -- the P tile of the same step
     uint8_t v[kTileBytes];
     __half ks[D], kz[D];  // per-dim scale / zero point of the K tile, in tile dim order
     uint64_t bar_s, bar_o;
     uint32_t tmem_base;
     int row_pos[kM];
-    float half_max[2][kM];  // row maximum over each half of the keys of the step
-    float half_sum[kM];     // running sum of the second half, for the partial
+    int flags[4];
 };
 
 // Byte offset of element (row, col) in a [128 rows][128 cols] fp16 tile stored as two 64-column blocks of
@@ -72,18 +70,18 @@ __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c
     return r;
 }
 
-// De-quantise half a key row (32 code bytes, dims 64 half .. 64 half + 63) into the tile: out = code * scale + zp,
-// pairs (d, d+4).  kPerDim: scale / zp pairs come from the per-dim tables (K); otherwise s2 / z2 hold the key's pair (V).
+// De-quantise one key row (64 code bytes) into the tile: out = code * scale + zp, pairs (d, d+4).
+// kPerDim: scale / zp pairs come from the per-dim tables (K); otherwise s2 / z2 hold the key's pair (V).
 template <bool kPerDim>
-__device__ __forceinline__ void dequant_row(const uint4 (&codes)[2], uint8_t* tile, int row, int half, const PrefillSmem& sm,
+__device__ __forceinline__ void dequant_row(const uint4 (&codes)[4], uint8_t* tile, int row, const PrefillSmem& sm,
                                             uint32_t s2, uint32_t z2) {
 #pragma unroll
-    for (int v4 = 0; v4 < 2; ++v4) {
+    for (int v4 = 0; v4 < 4; ++v4) {
         const uint4 pk = codes[v4];
         const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int chunk = half * 8 + v4 * 4 + i;  // dims 8 chunk .. 8 chunk + 7
+            const int chunk = v4 * 4 + i;  // dims 8 chunk .. 8 chunk + 7
             uint32_t u[4];
             unpack8(w[i], u);
             uint4 out;
@@ -100,11 +98,10 @@ __device__ __forceinline__ void dequant_row(const uint4 (&codes)[2], uint8_t* ti
     }
 }
 
-// Copy half an un-quantised fp16 row of the stage into the tile (dims re-ordered inside every group of eight).
-__device__ __forceinline__ void stage_row_to_tile(const __half* __restrict__ src, uint8_t* tile, int row, int half, bool live) {
+// Copy one un-quantised fp16 row of the stage into the tile (dims re-ordered inside every group of eight).
+__device__ __forceinline__ void stage_row_to_tile(const __half* __restrict__ src, uint8_t* tile, int row, bool live) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        const int chunk = half * 8 + c;
+    for (int chunk = 0; chunk < 16; ++chunk) {
         uint4 r = live ? reinterpret_cast<const uint4*>(src)[chunk] : make_uint4(0, 0, 0, 0);
         *reinterpret_cast<uint4*>(tile + tile_off(row, 8 * chunk)) =
             make_uint4(prmt(r.x, r.z, 0x5410), prmt(r.x, r.z, 0x7632), prmt(r.y, r.w, 0x5410), prmt(r.y, r.w, 0x7632));
@@ -117,7 +114,6 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     PrefillSmem& sm = *reinterpret_cast<PrefillSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
     const LayerView& L = P.L;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row = tid & (kM - 1), half = tid >> 7;  // this thread's query row / key row, and which half of it
     const int mt = blockIdx.x, head = blockIdx.y, zs = blockIdx.z;
     const int G = L.q_heads / L.kv_heads;
     const int kv_total = *P.total_pos + 1;
@@ -127,6 +123,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         mbar_init(&sm.bar_s, 1);
         mbar_init(&sm.bar_o, 1);
         mbar_fence_init();
+        sm.flags[0] = 0;
     }
     // ---- Q tile: rotate, scale, fp16, tile dim order.  One warp per row, lane l holds dims l + 32 j.
     for (int r = warp; r < kM; r += kThreads / 32) {
@@ -150,14 +147,14 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + kN;
-    const uint32_t lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;  // a warp reaches the TMEM lanes of its index mod 4
+    const uint32_t lane_base = static_cast<uint32_t>(32 * warp) << 16;
 
     int max_pos = -1, min_pos = INT_MAX;
     for (int r = 0; r < kM; ++r) {
         const int p = sm.row_pos[r];
         if (p >= 0) { max_pos = max(max_pos, p); min_pos = min(min_pos, p); }
     }
-    const int my_pos = sm.row_pos[row];
+    const int my_pos = sm.row_pos[tid];
     // key tiles this CTA walks: those a row of the tile can see, cut into ksplit ranges
     const int ntiles = max_pos < 0 ? 0 : min((kv_total + kN - 1) / kN, max_pos / kN + 1);
     const int t0 = static_cast<int>(static_cast<int64_t>(ntiles) * zs / P.ksplit);
@@ -174,7 +171,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     // Everything a tile needs from global memory before its K side can be de-quantised; fetched one tile ahead
     // so that the page-table lookup and the load latency hide behind the previous tile's softmax.
     struct KFetch {
-        uint4 codes[2], vcodes[2];
+        uint4 codes[4], vcodes[4];
         uint32_t vsz;
         __half ks, kz;
         int32_t page;  // page of this thread's key (-1: tile unusable)
@@ -187,18 +184,18 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         if (!f.ok || !f.sealed) return;
         const int32_t pg0 = L.page_of(tbl, 2 * t), pg1 = L.page_of(tbl, 2 * t + 1);
         if (pg0 < 0 || pg1 < 0) { f.ok = false; return; }  // reported in the error word; every thread skips the tile alike
-        f.page = row < 64 ? pg0 : pg1;
-        const uint4* kc = reinterpret_cast<const uint4*>(L.k_code + page_head_offset(64, L.kv_heads, f.page, head) + (row & 63) * 64 + half * 32);
+        f.page = tid < 64 ? pg0 : pg1;
+        const uint4* kc = reinterpret_cast<const uint4*>(L.k_code + page_head_offset(64, L.kv_heads, f.page, head) + (tid & 63) * 64);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) f.codes[i] = kc[i];
-        const uint4* vc = reinterpret_cast<const uint4*>(L.v_code + page_head_offset(64, L.kv_heads, f.page, head) + (row & 63) * 64 + half * 32);
+        for (int i = 0; i < 4; ++i) f.codes[i] = kc[i];
+        const uint4* vc = reinterpret_cast<const uint4*>(L.v_code + page_head_offset(64, L.kv_heads, f.page, head) + (tid & 63) * 64);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) f.vcodes[i] = vc[i];
-        f.vsz = *reinterpret_cast<const uint32_t*>(L.v_scale + page_head_offset(4, L.kv_heads, f.page, head) + (row & 63) * 4 + 2);
-        // per-dim scale / zero point of the tile (stored in both pages): page row d/2 = [s s z z other]; dim = row
+        for (int i = 0; i < 4; ++i) f.vcodes[i] = vc[i];
+        f.vsz = *reinterpret_cast<const uint32_t*>(L.v_scale + page_head_offset(4, L.kv_heads, f.page, head) + (tid & 63) * 4 + 2);
+        // per-dim scale / zero point of the tile (stored in both pages): page row d/2 = [s s z z other]
         const __half* ksp = L.k_scale + page_head_offset(5, L.kv_heads, pg0, head);
-        f.ks = ksp[(row >> 1) * 5 + (row & 1)];
-        f.kz = ksp[(row >> 1) * 5 + 2 + (row & 1)];
+        f.ks = ksp[(tid >> 1) * 5 + (tid & 1)];
+        f.kz = ksp[(tid >> 1) * 5 + 2 + (tid & 1)];
     };
     KFetch cur, nxt;
     fetch_k(t0, nxt);
@@ -209,17 +206,17 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         const bool sealed = cur.sealed;
         if (!cur.ok) { fetch_k(t + 1, nxt); tables_ready = false; continue; }
         if (!tables_ready) {
-            if (sealed && half == 0) {
-                sm.ks[dim_slot(row)] = cur.ks;
-                sm.kz[dim_slot(row)] = cur.kz;
+            if (sealed) {
+                sm.ks[dim_slot(tid)] = cur.ks;
+                sm.kz[dim_slot(tid)] = cur.kz;
             }
             __syncthreads();  // scale tables visible
         }
         // ---- K tile -> shared memory (the previous P V does not touch the K buffer: P lives in tensor memory)
         if (sealed) {
-            dequant_row<true>(cur.codes, sm.k, row, half, sm, 0, 0);
+            dequant_row<true>(cur.codes, sm.k, tid, sm, 0, 0);
         } else {
-            stage_row_to_tile(L.stage_row(0, t & 1, head, row), sm.k, row, half, base + row < kv_total);
+            stage_row_to_tile(L.stage_row(0, t & 1, head, tid), sm.k, tid, base + tid < kv_total);
         }
         // ---- the previous P V reads P from the columns S = Q K^T is about to overwrite, and the V buffer: drain it
         if (have_o && !mbar_wait_bounded(&sm.bar_o, (it - 1) & 1)) { failed = true; }
@@ -236,77 +233,83 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         }
         // ---- V tile -> shared memory (overlaps the QK MMA), then start fetching the next tile
         if (sealed) {
-            dequant_row<false>(cur.vcodes, sm.v, row, half, sm, prmt(cur.vsz, cur.vsz, 0x1010), prmt(cur.vsz, cur.vsz, 0x3232));
+            dequant_row<false>(cur.vcodes, sm.v, tid, sm, prmt(cur.vsz, cur.vsz, 0x1010), prmt(cur.vsz, cur.vsz, 0x3232));
         } else {
-            stage_row_to_tile(L.stage_row(1, t & 1, head, row), sm.v, row, half, base + row < kv_total);
+            stage_row_to_tile(L.stage_row(1, t & 1, head, tid), sm.v, tid, base + tid < kv_total);
         }
         fetch_k(t + 1, nxt);  // (issuing this at the top of the step was measured slower)
-        // ---- softmax of row `row`, keys base + 64 half .. + 63
+        // ---- softmax of row `tid`
         if (!mbar_wait_bounded(&sm.bar_s, it & 1)) { failed = true; }  // a warp that gave up reads stale S; the CTA agrees below
         tc::fence_after_sync();
         if (warp_has_rows) {
-        float s[kN / 2];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            uint32_t r[32];
-            tc::tmem_ld32(tmem_s + lane_base + 64 * half + 32 * c, r);
+        float s[kN];
+        {  // the four loads are in flight together: one round trip to tensor memory, not four
+            uint32_t r0[32], r1[32], r2[32], r3[32];
+            tc::tmem_ld32(tmem_s + lane_base, r0);
+            tc::tmem_ld32(tmem_s + lane_base + 32, r1);
+            tc::tmem_ld32(tmem_s + lane_base + 64, r2);
+            tc::tmem_ld32(tmem_s + lane_base + 96, r3);
             tc::tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) s[32 * c + j] = __uint_as_float(r[j]);
+            for (int j = 0; j < 32; ++j) {
+                s[j] = __uint_as_float(r0[j]);
+                s[32 + j] = __uint_as_float(r1[j]);
+                s[64 + j] = __uint_as_float(r2[j]);
+                s[96 + j] = __uint_as_float(r3[j]);
+            }
         }
-        const int key0 = base + 64 * half;
         if (base + kN - 1 > min_pos || !sealed) {
 #pragma unroll
-            for (int j = 0; j < kN / 2; ++j)
-                if (key0 + j > my_pos || key0 + j >= kv_total) s[j] = -INFINITY;
+            for (int j = 0; j < kN; ++j)
+                if (base + j > my_pos || base + j >= kv_total) s[j] = -INFINITY;
         }
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the scheduler has few warps to hide a serial one
+        float mx = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < kN / 2; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
-        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        // both halves of the row have S in registers from here on: the pair agrees on the maximum, and either may
-        // overwrite columns of S with P
-        sm.half_max[half][row] = mx;
-        named_barrier_sync(1 + (warp & 3), 64);
-        mx = fmaxf(mx, sm.half_max[half ^ 1][row]);
-        const float m_new = fmaxf(m_run, mx);
+        for (int j = 0; j < kN; ++j) mx = fmaxf(mx, s[j]);
+        // The reference point of the row's exponentials follows the running maximum lazily: it moves only when the
+        // maximum has grown by more than 2^kLazy, so P stays below 2^kLazy (exact enough in fp16, whose precision is
+        // relative) and the O accumulator is rescaled a few times per walk instead of at every new maximum.
+        constexpr float kLazy = 8.0f;
+        const bool grown = mx > m_run + kLazy || (m_run == -INFINITY && mx > -INFINITY);
+        const float m_new = grown ? mx : m_run;
         const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-        const float alpha = fast_exp2(m_run - m_use);
-        const bool moved = have_o && m_new > m_run;
+        const float alpha = grown ? fast_exp2(m_run - m_use) : 1.0f;
+        const bool moved = have_o && grown;
         m_run = m_new;
-        float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        // P stays in tensor memory: fp16 pairs over the first 64 columns of S, the A operand of the P V product -- no
-        // shared-memory round trip for P.  Keys 64 half + 2 j, + 1 -> column 32 half + j.
-        {
+        float sum = 0.0f;
+        // P stays in tensor memory: fp16 pairs over the first 64 columns of S (already in registers), the A operand
+        // of the P V product -- no shared-memory round trip for P
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
             uint32_t pk[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const float p0 = fast_exp2(s[2 * j] - m_use), p1 = fast_exp2(s[2 * j + 1] - m_use);
-                sum4[j & 3] += p0 + p1;
+                const float p0 = fast_exp2(s[64 * c + 2 * j] - m_use), p1 = fast_exp2(s[64 * c + 2 * j + 1] - m_use);
+                sum += p0 + p1;
                 pk[j] = pack_half2(p0, p1);
             }
-            tc::tmem_st32(tmem_s + lane_base + 32 * half, pk);
+            tc::tmem_st32(tmem_s + lane_base + 32 * c, pk);
         }
         tc::tmem_st_wait();
-        l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-        if (__any_sync(0xffffffffu, moved)) {  // rescale this thread's 64 dims of O (alpha = 1 for rows that did not move)
+        l_run = l_run * alpha + sum;
+        if (__any_sync(0xffffffffu, moved)) {  // rescale this warp's 32 rows of O (alpha = 1 for rows that did not move)
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 uint32_t r[32];
-                tc::tmem_ld32(tmem_o + lane_base + 64 * half + 32 * c, r);
+                tc::tmem_ld32(tmem_o + lane_base + 32 * c, r);
                 tc::tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
-                tc::tmem_st32(tmem_o + lane_base + 64 * half + 32 * c, r);
+                tc::tmem_st32(tmem_o + lane_base + 32 * c, r);
             }
             tc::tmem_st_wait();
         }
         }  // warp_has_rows (rows of the other warps are never read: their P and O may hold anything)
         // the scale tables of the next tile: this tile's K rows were de-quantised two barriers ago
         tables_ready = nxt.ok;
-        if (nxt.ok && nxt.sealed && half == 0) {
-            sm.ks[dim_slot(row)] = nxt.ks;
-            sm.kz[dim_slot(row)] = nxt.kz;
+        if (nxt.ok && nxt.sealed) {
+            sm.ks[dim_slot(tid)] = nxt.ks;
+            sm.kz[dim_slot(tid)] = nxt.kz;
         }
         // ---- O += P V (every warp has its V rows in shared memory and its P rows in tensor memory; any failed wait ends the walk)
         fence_proxy_async();
@@ -328,20 +331,18 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     tc::fence_after_sync();
 
     // ---- partial of this (row tile, key range): m (log2 units), l, o in tile dim order
-    const int64_t idx = ((static_cast<int64_t>(head) * P.mtiles + mt) * P.ksplit + zs) * kM + row;
-    if (half == 1) sm.half_sum[row] = l_run;
-    __syncthreads();
-    if (my_pos >= 0 && half == 0) {
+    const int64_t idx = ((static_cast<int64_t>(head) * P.mtiles + mt) * P.ksplit + zs) * kM + tid;
+    if (my_pos >= 0) {
         P.ws_m[idx] = failed ? -INFINITY : m_run;
-        P.ws_l[idx] = failed ? 0.0f : l_run + sm.half_sum[row];
+        P.ws_l[idx] = failed ? 0.0f : l_run;
     }
-    float* orow = P.ws_o + idx * D + 64 * half;
+    float* orow = P.ws_o + idx * D;
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
+    for (int c = 0; c < 4; ++c) {
         if (!warp_has_rows) break;
         uint32_t r[32];
         if (have_o) {
-            tc::tmem_ld32(tmem_o + lane_base + 64 * half + 32 * c, r);
+            tc::tmem_ld32(tmem_o + lane_base + 32 * c, r);
             tc::tmem_ld_wait();
         }
         if (my_pos < 0) continue;
@@ -377,13 +378,25 @@ __global__ void __launch_bounds__(256) prefill_merge_kernel(const float* __restr
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     float l = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (m != -INFINITY) {
-#pragma unroll 4
-        for (int z = warp; z < ksplit; z += 8) {
-            const int64_t i = base + static_cast<int64_t>(z) * kM;
-            const float w = fast_exp2(ws_m[i] - m);
-            l += w * ws_l[i];
+        for (int z0 = warp; z0 < ksplit; z0 += 64) {  // eight ranges of the warp at a time, every load issued before the first use
+            float pm[8], pl[8], po[8][4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o[j] += w * ws_o[i * D + dim_slot(lane + 32 * j)];
+            for (int k = 0; k < 8; ++k) {
+                const int z = z0 + 8 * k;
+                const bool on = z < ksplit;
+                const int64_t i = base + static_cast<int64_t>(on ? z : z0) * kM;
+                pm[k] = on ? ws_m[i] : -INFINITY;
+                pl[k] = ws_l[i];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) po[k][j] = ws_o[i * D + dim_slot(lane + 32 * j)];
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float w = fast_exp2(pm[k] - m);  // 0 for a range that is not there
+                l += w * pl[k];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) o[j] += w * po[k][j];
+            }
         }
     }
 #pragma unroll

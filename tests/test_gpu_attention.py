@@ -240,7 +240,7 @@ def test_chunk_partials_of_two_range_caches_merge_to_the_full_answer(prefix, chu
     assert ok, msg
 
 
-@pytest.mark.parametrize("prefix,chunk", [(333, 100), (0, 128), (1000, 300), (120, 8), (256, 1024), (77, 1)])
+@pytest.mark.parametrize("prefix,chunk", [(333, 100), (0, 128), (1000, 300), (120, 8), (3000, 20), (256, 1024), (77, 1)])
 def test_prefill_chunk(prefix, chunk):
     """Quantise-append a chunk, then causal chunk attention over prefix + chunk on the tcgen05 kernel.  Covers a
     chunk that starts the cache, chunks that complete tiles, an open tile left in the stage, a 1,024-token chunk."""
