@@ -35,9 +35,10 @@ sys.path.insert(0, ROOT)
 D, H, QH, LAYERS = 128, 4, 24, 16
 LONG_CTX = 378944
 # DRAM bytes (read + write) one decode call moves per token of context, from an ncu capture of attn_kernel at 131,072
-# tokens: the layout's bytes (146 B per token and KV head, the per-dim scales being stored in both pages of a tile)
-# plus the partials written; traffic grows in proportion to the context (same pages per token, same splits per SM).
-TRAFFIC_BYTES_PER_TOKEN = 602.3
+# tokens (74.57 MB read + 1.33 MB written): the codes and axes the kernel fetches (the second page's copy of the per-dim
+# scales is skipped) plus the partials written; traffic grows in proportion to the context (same pages per token, same
+# splits per SM).
+TRAFFIC_BYTES_PER_TOKEN = 579.1
 SEALED_B, TAIL_B = 140, 512  # algorithmic bytes per sealed / open-tile token per KV head (codes + 12 B of axes | fp16 K+V rows)
 
 
