@@ -91,6 +91,18 @@ int kvb_append(const kvb_layer* layer, const void* k, const void* v, const int32
  * Replaces kvarn128_decode_tile (LAUNCH.h:56-58, LAUNCH.cu:1099-1115). */
 int kvb_decode_tile(const kvb_layer* layer, int tile, int head, void* out_k, void* out_v, void* stream);
 
+/* The compact tile record at every code width of the reference (bits = 2, 3, 4, 5, 6 or 8): each 128 x 128 fp32 matrix
+ * (a K tile with the dims as rows, a V tile with the tokens as rows, as the caller lays it out) becomes
+ *     payload (LSB-first bit string, row-major, 16 * bits bytes per row) || scale_axis[128] || zp_axis[128] || other_axis[128]
+ * (axes fp16), kvb_record_bytes(bits) = 2048 * bits + 768 bytes: 140 B per token and KV head for K4V4, 108 B for K4V2.
+ * No variance balancing (other_axis = 1): codes and axes equal the host oracle's bit for bit
+ * (kvarn-evidence/oracle/bee_oracle.cpp:152-172 bit string, :309-357 quantiser, :359-374 inverse; the engine's kernels are
+ * templated on the same widths, kvarn128_launch.cu:126,158,248).  tiles: [n_tiles][128][128] fp32; records:
+ * n_tiles * kvb_record_bytes(bits) bytes; all device memory.  The attention entry points read 4-bit P1 planes only. */
+size_t kvb_record_bytes(int bits);
+int kvb_records_encode(const float* tiles, int n_tiles, int bits, void* records, void* stream);
+int kvb_records_decode(const void* records, int n_tiles, int bits, float* tiles, void* stream);
+
 /* Split count and workspace size for the attention calls.
  * Replace causal_attention_split_capacity (P3:3326-3380) and the partial_acc/partial_m/partial_l tensors
  * the reference's callers allocate (P3:3612-3616). rows = query tokens per call (1 decode, 1..8 verify). */

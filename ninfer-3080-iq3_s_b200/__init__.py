@@ -14,7 +14,7 @@ from .build import build  # noqa: F401
 
 
 def __getattr__(name):
-    if name in ("sharded", "dump"):
+    if name in ("sharded", "dump", "records"):
         import importlib
 
         return importlib.import_module(__name__ + "." + name)

@@ -9,11 +9,11 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libkvarn_b200.so")
-SOURCES = ["kvb_api.cu", "kvb_append.cu", "kvb_attn.cu", "kvb_attn_general.cu", "kvb_prefill.cu"]
+SOURCES = ["kvb_api.cu", "kvb_append.cu", "kvb_attn.cu", "kvb_attn_general.cu", "kvb_prefill.cu", "kvb_record.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
 # per-file flags: the codec must not contract a*b+c (bit-exact codes), the attention kernels may
-EXTRA = {"kvb_append.cu": ["-fmad=false"]}
+EXTRA = {"kvb_append.cu": ["-fmad=false"], "kvb_record.cu": ["-fmad=false"]}
 
 
 def _stale(target, deps):

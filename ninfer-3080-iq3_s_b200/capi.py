@@ -45,6 +45,9 @@ SYMBOLS = {
     "kvb_plane_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "kvb_append": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "kvb_decode_tile": (C.c_int, [C.POINTER(kvb_layer), C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "kvb_record_bytes": (C.c_size_t, [C.c_int]),
+    "kvb_records_encode": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "kvb_records_decode": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "kvb_split_capacity": (C.c_int, [C.c_int] * 5),
     "kvb_workspace_bytes": (C.c_size_t, [C.c_int] * 6),
     "kvb_attn_decode": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p,

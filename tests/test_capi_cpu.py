@@ -28,6 +28,11 @@ def test_sizes():
     assert lib.kvb_stage_bytes(256, 4) == 1 << 20
     assert [lib.kvb_plane_bytes(w, 128, 4, 2) for w in range(4)] == [4096 * 8, 640 * 8, 4096 * 8, 512 * 8]
     assert [lib.kvb_plane_bytes(w, 256, 1, 1) for w in range(4)] == [8192, 1280, 8192, 1024]
+    assert [lib.kvb_record_bytes(b) for b in (2, 3, 4, 5, 6, 8)] == [2048 * b + 768 for b in (2, 3, 4, 5, 6, 8)]
+    assert lib.kvb_record_bytes(1) == 0 and lib.kvb_record_bytes(7) == 0
+    assert lib.kvb_records_encode(None, 0, 4, None, None) == 0  # nothing to do: no launch
+    assert lib.kvb_records_encode(None, 1, 4, None, None) == pkg().capi.KVB_EINVAL
+    assert lib.kvb_records_decode(None, 0, 7, None, None) == pkg().capi.KVB_EINVAL
     assert lib.kvb_split_capacity(32768, 4, 24, 1, 1) >= 2
     assert lib.kvb_workspace_bytes(32768, 4, 24, 128, 1, 1) > 0
 
