@@ -511,7 +511,8 @@ def measure_decode_ctx(E, args):
     torch = E.torch
     ctx = args.ctx or 131072
     layers_n = args.layers or max(2, min(16, int(400e6 // (ctx * H * 146)) + 1))
-    layers = [E.layer(ctx, 8, i) for i in range(layers_n)]
+    iters = getattr(args, "iters", 0)  # > 0: caches written with that many Sinkhorn iterations (per-key / per-dim factors in the kernel)
+    layers = [E.layer(ctx, 8, i, iters=iters) for i in range(layers_n)]
     q = torch.randn((layers_n, QH, D), generator=E.gen, device=E.dev).to(torch.float16)
     pos = torch.full((1,), ctx - 1, dtype=torch.int32, device=E.dev)
     outs = torch.empty((layers_n, QH, D), dtype=torch.float16, device=E.dev)
@@ -534,7 +535,7 @@ def measure_decode_ctx(E, args):
         "metric": "decode_attn_hbm_gbs", "value": nbytes / (us * 1e-6) / 1e9, "unit": "GB/s", "n_gpus": E.world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "us_per_layer": us, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": f"decode_attention_only_ctx{ctx}", "layers": layers_n, "q_heads": QH, "kv_heads": H, "head_dim": D,
+        "config": {"workload": f"decode_attention_only_ctx{ctx}" + (f"_sinkhorn{iters}" if iters else ""), "layers": layers_n, "q_heads": QH, "kv_heads": H, "head_dim": D,
                    "l2": f"{layers_n} layers x {ctx * H * 146 / 1e6:.0f} MB between revisits"},
         "roofline": {"bound": "hbm", "achieved": nbytes / (us * 1e-6) / 1e9, "peak": peak, "peak_kind": kind, "unit": "GB/s",
                      "frac": nbytes / (us * 1e-6) / 1e9 / peak, "traffic": TRAFFIC_BYTES_PER_TOKEN * ctx if D == 128 else None},
@@ -776,7 +777,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="layers held (long379k: 16; decodectx: sized to exceed L2; verify131k: 4)")
     ap.add_argument("--no-blocks", dest="blocks", action="store_false", help="long379k on one GPU: skip the other workloads' blocks")
     ap.add_argument("--chunk", type=int, default=0, help="append: tokens per append call (default 1024)")
-    ap.add_argument("--iters", type=int, default=0, help="append: Sinkhorn iterations of the encoder (0 = bit-exact regime, 16 = engine default)")
+    ap.add_argument("--iters", type=int, default=0, help="append, decodectx: Sinkhorn iterations of the encoder (0 = bit-exact regime, 16 = engine default)")
     ap.add_argument("--head-dim", type=int, default=128, choices=[128, 256],
                     help="decodectx / append: 256 is the reference engine's own geometry")
     ap.add_argument("--ctx", type=int, default=0, help="context for decodectx (default 131072) / prefix length for prefill262k (default 262144)")

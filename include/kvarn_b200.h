@@ -178,7 +178,7 @@ int kvb_merge_partials_packed(const float* packed, int parts, int q_heads, int h
  * A wait that runs out sets KVB_ERR_WAIT_TIMEOUT in *layer->error_word and writes zeros; nothing traps or hangs.
  * `state` is three zero-initialised device words owned by this rank.  Ring buffer and state must be zeroed once
  * before the first call; all ranks must make the same sequence of calls on a ring; calls on one ring must not
- * overlap on the GPU.  head_dim 128, sinkhorn_iters 0, at most 16 ranks. */
+ * overlap on the GPU.  head_dim 128, at most 16 ranks. */
 typedef struct kvb_peer_ring {
     void* const* peer_bufs;
     void* local_buf;

@@ -332,7 +332,10 @@ __device__ __forceinline__ void process_stage_group(const __half* krow, const __
 // the workspace.  NB = 8-row blocks of query rows per warp.  A pass = one page: its 64 logits per row are held at
 // once.  Within a page the keys are taken in a fixed permutation (see key_lo below) that lets the QK accumulators
 // feed the PV operands of the shifted V sub-blocks without any re-ordering.
-template <int NB, int W>
+// kOther: the cache was written with variance balancing (Sinkhorn iterations > 0): every key carries a factor other_K on
+// its logits and every dim of a tile a factor other_V on its output (reference kvarn128_codec.cuh:331-347); both are 1
+// otherwise and the arithmetic for them is compiled out.
+template <int NB, int W, bool kOther = false>
 __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int head, int zb, int64_t pidx) {
     constexpr int kWarps = W, kThreads = W * 32;
     constexpr int kGroups = kPage / 16;            // 16-key groups of a page
@@ -431,7 +434,7 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
                 }
             } else {
                 const int lp = w0 + (n >> 1);
-                const bool with_k = (lp & 1) == 0 || lp == w0;  // K scale rows: with the first page of a tile this warp reads
+                const bool with_k = kOther || (lp & 1) == 0 || lp == w0;  // K scale rows: with the first page of a tile this warp reads (their fifth column is other_K of the page's own keys: always, when it is not 1)
                 uint8_t* hdr = R.hdr[(n >> 1) % kHdrs];
                 mbar_expect_tx(&R.bars[slot], kChunkBytes + kHdrV + (with_k ? kHdrK : 0));
                 bulk_g2s(dst, kc + static_cast<size_t>(pid) * code_stride, kChunkBytes, &R.bars[slot]);
@@ -530,6 +533,7 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
     const int key_lo = 16 * (g >> 1) + (g & 1);  // + 8 (grp >> 1) + 4 (grp & 1): key of m-row g; m-row g + 8 is 2 keys further
 
     QInt<NB> qi;
+    float ov[4][2][2];  // kOther: other_V of dims 32 db + 4g + xy + 2h of the current tile
     int cur_tile = -1;
     for (int pi = 0; pi < npages; ++pi) {
         const int lp = w0 + pi;
@@ -549,6 +553,16 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
             transpose_k_scale(hdr + kHdrV, R, lane);
             __syncwarp();
             build_qint<NB>(sm, R, lane, qi);
+            if constexpr (kOther) {  // other_V of the lane's 16 dims: V scale row d / 2 starts with (other(d even), other(d odd))
+#pragma unroll
+                for (int db = 0; db < 4; ++db)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const float2 o2 = unpack_half2(*reinterpret_cast<const uint32_t*>(hdr + (16 * db + 2 * g + h) * 8));
+                        ov[db][0][h] = o2.x;
+                        ov[db][1][h] = o2.y;
+                    }
+            }
         }
         const int first = lp * kPage;
         const bool need_mask = first + kPage - 1 > min_lim || first < key_begin || first + kPage > key_end;
@@ -606,6 +620,7 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
         }
         // ---- softmax of the page relative to its own row maxima; weights of the page against the running state
         float wq[NB][2];     // weight of the integer sums of this page in the running accumulators
+        float zfull[NB][2];  // kOther: sum over the page's keys of p * zp_V, weighted like the integer sums
         uint32_t bh[NB][kGroups], bl[NB][kGroups];  // 16-bit weights as B fragments: high and low bytes
         {
             // per-key scale of V: the largest of the page bounds p * scale_V; one factor for all rows
@@ -616,6 +631,51 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
             const float F = svmax > 0.0f ? kPMax / svmax : 0.0f, invF = svmax * (1.0f / kPMax);
             float alpha[NB][2], wpass[NB][2], cst[NB][2];
             bool moved = false;
+            float sl[NB][kGroups][4];  // logits relative to the page maximum (log2 units)
+            if constexpr (kOther) {
+                // logits = other_K(key) * (f * integer sum + qz): the page maximum is taken on the floats
+                float ok[kGroups][2];
+#pragma unroll
+                for (int grp = 0; grp < kGroups; ++grp)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                        ok[grp][h] = __half2float(*reinterpret_cast<const __half*>(hdr + kHdrV + (key_lo + 8 * (grp >> 1) + 4 * (grp & 1) + 2 * h) * 10 + 8));
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int grp = 0; grp < kGroups; ++grp)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            sl[nb][grp][e] = tot[nb][grp][e] == INT_MIN ? -INFINITY
+                                                                         : fmaf(static_cast<float>(tot[nb][grp][e]), qi.f[nb][e & 1], qi.qz[nb][e & 1]) * ok[grp][e >> 1];
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        float mpass = -INFINITY;
+#pragma unroll
+                        for (int grp = 0; grp < kGroups; ++grp) mpass = fmaxf(mpass, fmaxf(sl[nb][grp][j], sl[nb][grp][2 + j]));
+                        mpass = fmaxf(mpass, __shfl_xor_sync(0xffffffffu, mpass, 4));
+                        mpass = fmaxf(mpass, __shfl_xor_sync(0xffffffffu, mpass, 8));
+                        mpass = fmaxf(mpass, __shfl_xor_sync(0xffffffffu, mpass, 16));
+                        const float mnew = fmaxf(acc.m[nb][j], mpass);
+                        moved |= mnew > acc.m[nb][j];
+                        const float muse = mnew == -INFINITY ? 0.0f : mnew;
+                        alpha[nb][j] = fast_exp2(acc.m[nb][j] - muse);
+                        wpass[nb][j] = fast_exp2(mpass - muse);
+                        cst[nb][j] = mpass == -INFINITY ? 0.0f : mpass;
+                        acc.m[nb][j] = mnew;
+                        wq[nb][j] = wpass[nb][j] * invF;
+                    }
+                }
+                if (__any_sync(0xffffffffu, moved)) rescale<NB>(acc, alpha);
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int grp = 0; grp < kGroups; ++grp)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) sl[nb][grp][e] -= cst[nb][e & 1];  // masked keys stay at -inf
+            } else {
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
@@ -638,7 +698,6 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
                 }
             }
             if (__any_sync(0xffffffffu, moved)) rescale<NB>(acc, alpha);
-            float sl[NB][kGroups][4];  // logits relative to the page maximum (log2 units)
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
@@ -656,6 +715,7 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
                         for (int nb = 0; nb < NB; ++nb)
                             if (out || p > row_lim[nb][e & 1]) sl[nb][grp][e] = -INFINITY;
                     }
+            }
             }
             float lp_[NB][2], zp_[NB][2];
 #pragma unroll
@@ -689,7 +749,15 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     acc.l[nb][j] = fmaf(lp_[nb][j], wpass[nb][j], acc.l[nb][j]);
-                    acc.z[nb][j] = fmaf(zp_[nb][j], wpass[nb][j], acc.z[nb][j]);
+                    if constexpr (kOther) {  // the zero-point term takes other_V of the tile per dim: it enters the accumulators with the page
+                        float zs = zp_[nb][j];
+                        zs += __shfl_xor_sync(0xffffffffu, zs, 4);
+                        zs += __shfl_xor_sync(0xffffffffu, zs, 8);
+                        zs += __shfl_xor_sync(0xffffffffu, zs, 16);
+                        zfull[nb][j] = zs * wpass[nb][j];
+                    } else {
+                        acc.z[nb][j] = fmaf(zp_[nb][j], wpass[nb][j], acc.z[nb][j]);
+                    }
                 }
         }
         // ---- PV on the int8 path.  Matrix i' of the page (8 rows) gathers keys 2i', 2i'+1 of each of the four sub-blocks:
@@ -742,7 +810,12 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
 #pragma unroll
                             for (int c = 0; c < 4; ++c) {
                                 const float v = static_cast<float>((ix[nb][d][xy][0][c] << 8) + ix[nb][d][xy][1][c]);
-                                acc.o[nb][sweep * kDb + d][xy][c] = fmaf(v, xy ? wq[nb][c & 1] * 0.0625f : wq[nb][c & 1], acc.o[nb][sweep * kDb + d][xy][c]);
+                                if constexpr (kOther) {  // (sum p code scale_V + sum p zp_V) * other_V(dim)
+                                    const float tv = fmaf(v, xy ? wq[nb][c & 1] * 0.0625f : wq[nb][c & 1], zfull[nb][c & 1]);
+                                    acc.o[nb][sweep * kDb + d][xy][c] = fmaf(tv, ov[sweep * kDb + d][xy][c >> 1], acc.o[nb][sweep * kDb + d][xy][c]);
+                                } else {
+                                    acc.o[nb][sweep * kDb + d][xy][c] = fmaf(v, xy ? wq[nb][c & 1] * 0.0625f : wq[nb][c & 1], acc.o[nb][sweep * kDb + d][xy][c]);
+                                }
                             }
             }
         }
@@ -808,11 +881,11 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
     }
 }
 
-template <int NB, int W>
+template <int NB, int W, bool kOther = false>
 __global__ void __launch_bounds__(W * 32, 1) attn_kernel(const AttnParams P) {
     grid_dependency_wait();  // q, the positions and the cache come from the kernels before this one
     const int head = blockIdx.y, zb = blockIdx.z, split = blockIdx.x;
-    attn_cta<NB, W>(P, split, head, zb, ((static_cast<int64_t>(head) * gridDim.z + zb) * P.nsplit + split) * kRows);
+    attn_cta<NB, W, kOther>(P, split, head, zb, ((static_cast<int64_t>(head) * gridDim.z + zb) * P.nsplit + split) * kRows);
 }
 
 // Batched decode: `n` independent sequences (their caches described by device-resident kvb_layer structs, same
@@ -1156,15 +1229,15 @@ int launch_general_attention(const kvb_layer* layer, const void* q, const int32_
 namespace {
 
 // One attention launch with W warps per CTA (the opt-in to large dynamic shared memory is made once per device and W).
-template <int NB, int W>
+template <int NB, int W, bool kOther = false>
 cudaError_t launch_attn(dim3 grid, cudaStream_t stream, const AttnParams& P) {
     constexpr int smem = static_cast<int>(sizeof(AttnSmem<W>));
     static unsigned long long opted = 0;
     if (first_call_on_device(opted)) {
-        const cudaError_t e = cudaFuncSetAttribute(attn_kernel<NB, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        const cudaError_t e = cudaFuncSetAttribute(attn_kernel<NB, W, kOther>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_early(attn_kernel<NB, W>, grid, dim3(W * 32), smem, stream, P);
+    return launch_early(attn_kernel<NB, W, kOther>, grid, dim3(W * 32), smem, stream, P);
 }
 
 // Warps per CTA for a decode call: 8, 12 or 16 (whole warp quartets: an SM hands registers and issue slots out per
@@ -1196,9 +1269,8 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     if (T < 1 || T > 8) return fail(KVB_ERANGE, "%s: %d query tokens (1..8 supported)", who, T);
     if (kv_len_max < 1) return fail(KVB_EINVAL, "%s: kv_len_max %d", who, kv_len_max);
     if (layer->stage == nullptr) return fail(KVB_EINVAL, "%s: layer has no stage buffer", who);
-    if ((layer->head_dim != 128 || layer->sinkhorn_iters != 0) && push != nullptr)
-        return fail(KVB_ERANGE, "%s: the sharded decode covers head_dim 128 caches written with sinkhorn_iters = 0", who);
-    if (layer->head_dim != 128 || layer->sinkhorn_iters != 0)  // shapes outside the tuned kernels: general kernel, same semantics
+    if (layer->head_dim != 128 && push != nullptr) return fail(KVB_ERANGE, "%s: the sharded decode covers head_dim 128", who);
+    if (layer->head_dim != 128)  // two slices per key: general kernel, same semantics
         return launch_general_attention(layer, q, pos_dev, total_pos_dev, T, scale, kv_len_max, key_begin, key_end, workspace, out,
                                         part_m, part_l, part_o, stream);
     const int Z = zblocks_of(layer->q_heads, layer->kv_heads, T);
@@ -1220,7 +1292,13 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     P.ws_o = P.ws_l + rows;
     const bool upper = T * (layer->q_heads / layer->kv_heads) > 8;
     const dim3 grid(parts, layer->kv_heads, Z);
-    if (upper) {
+    if (layer->sinkhorn_iters != 0) {  // balanced caches: other_K per key, other_V per dim (more registers: 8 warps)
+        if (upper) {
+            KVB_CUDA_OK((launch_attn<2, kWarpsWide, true>(grid, stream, P)));
+        } else {
+            KVB_CUDA_OK((launch_attn<1, 8, true>(grid, stream, P)));
+        }
+    } else if (upper) {
         KVB_CUDA_OK((launch_attn<2, kWarpsWide>(grid, stream, P)));
     } else {
         switch (decode_warps(kv_len_max, nsplit)) {
@@ -1472,7 +1550,7 @@ extern "C" int kvb_attn_verify(const kvb_layer* layer, const void* q, const void
     if (width < 1 || width > 8) return kvb::fail(KVB_ERANGE, "kvb_attn_verify: width %d (1..8; the reference rejects more, too)", width);
     if (int st = kvb::check_layer(layer, "kvb_attn_verify")) return st;
     if (int st = kvb_append(layer, k, v, positions_dev, width, stream)) return st;
-    if (width * (layer->q_heads / layer->kv_heads) >= kDenseRows && layer->head_dim == 128 && layer->sinkhorn_iters == 0) {
+    if (width * (layer->q_heads / layer->kv_heads) >= kDenseRows && layer->head_dim == 128) {
         if (q == nullptr || workspace == nullptr || out == nullptr) return kvb::fail(KVB_EINVAL, "kvb_attn_verify: null q / workspace / out");
         return kvb::launch_chunk_attention(layer, q, positions_dev, width, scale, kv_len_max, workspace, out, static_cast<cudaStream_t>(stream),
                                            nullptr, nullptr, nullptr, nullptr);
@@ -1494,7 +1572,7 @@ extern "C" int kvb_attn_chunk_partial(const kvb_layer* layer, const void* q, con
         return fail(KVB_EINVAL, "kvb_attn_chunk_partial: null argument");
     if (layer->stage == nullptr) return fail(KVB_EINVAL, "kvb_attn_chunk_partial: layer has no stage buffer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (layer->head_dim != 128 || layer->sinkhorn_iters != 0)
+    if (layer->head_dim != 128)
         return launch_general_attention(layer, q, positions_dev, positions_dev + (tokens - 1), tokens, scale, kv_len_max, 0, INT_MAX, workspace,
                                         nullptr, part_m, part_l, part_o, st);
     if (tokens <= 8 && tokens * (layer->q_heads / layer->kv_heads) < kDenseRows)
@@ -1512,7 +1590,7 @@ extern "C" int kvb_attn_rows(const kvb_layer* layer, const void* q, const int32_
     if (int st = check_layer(layer, "kvb_attn_rows")) return st;
     if (total_pos_dev == nullptr) return fail(KVB_EINVAL, "kvb_attn_rows: null total_pos_dev");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (rows * (layer->q_heads / layer->kv_heads) >= kDenseRows && layer->head_dim == 128 && layer->sinkhorn_iters == 0) {
+    if (rows * (layer->q_heads / layer->kv_heads) >= kDenseRows && layer->head_dim == 128) {
         if (q == nullptr || positions_dev == nullptr || workspace == nullptr || out == nullptr)
             return fail(KVB_EINVAL, "kvb_attn_rows: null q / positions / workspace / out");
         return launch_chunk_attention(layer, q, positions_dev, rows, scale, kv_len_max, workspace, out, st, nullptr, nullptr, nullptr, total_pos_dev);

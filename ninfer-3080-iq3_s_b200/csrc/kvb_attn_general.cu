@@ -1,7 +1,8 @@
 // kvb_attn_general.cu -- attention over the quantised cache for the shapes the tuned kernels do not cover:
-// head_dim 256 (two 128-dim slices, the reference engine's own geometry) and caches written with Sinkhorn
-// iterations > 0 (per-key and per-dim `other` factors different from 1).  Same semantics and the same entry
-// points; a plain CUDA-core kernel: one CTA per (key range, KV head, query token), one warp per key, every
+// head_dim 256 (two 128-dim slices, the reference engine's own geometry) and, for prefill chunks and verify steps
+// of 32 merged rows or more, caches written with Sinkhorn iterations > 0 (per-key and per-dim `other` factors
+// different from 1; decode and narrower verify steps of such caches run on the int8 kernel).  Same semantics and
+// the same entry points; a plain CUDA-core kernel: one CTA per (key range, KV head, query token), one warp per key, every
 // element de-quantised as (q * scale_axis + zp_axis) * other_axis in fp32 (reference kvarn128_codec.cuh:331-347),
 // fp32 dot products with warp-shuffle reductions, running softmax per warp, log-sum-exp merges at the end.
 // Lane l owns the contiguous dims R l .. R l + R - 1 (R = head_dim / 32): its codes of a key are one 16- or 32-bit

@@ -50,6 +50,7 @@ struct __align__(1024) PrefillSmem {
     uint8_t k[kTileBytes];  // the K tile, then -- once S = Q K^T has completed -- the P tile of the same step
     uint8_t v[kTileBytes];
     __half ks[D], kz[D];  // per-dim scale / zero point of the K tile, in tile dim order
+    __half vo[D];         // per-dim other_V of the tile (balanced caches), in tile dim order
     uint64_t bar_s, bar_o;
     uint32_t tmem_base;
     int row_pos[kM];
@@ -69,12 +70,19 @@ __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c
     asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
     return r;
 }
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
 
 // De-quantise one key row (64 code bytes) into the tile: out = code * scale + zp, pairs (d, d+4).
 // kPerDim: scale / zp pairs come from the per-dim tables (K); otherwise s2 / z2 hold the key's pair (V).
+// `other` (caches written with variance balancing): the result is multiplied by the key's other_K (K: o2, both halves)
+// or by the per-dim other_V table (V), reference kvarn128_codec.cuh:331-347; fp16 like the rest of this kernel.
 template <bool kPerDim>
 __device__ __forceinline__ void dequant_row(const uint4 (&codes)[4], uint8_t* tile, int row, const PrefillSmem& sm,
-                                            uint32_t s2, uint32_t z2) {
+                                            uint32_t s2, uint32_t z2, bool other, uint32_t o2) {
 #pragma unroll
     for (int v4 = 0; v4 < 4; ++v4) {
         const uint4 pk = codes[v4];
@@ -90,8 +98,13 @@ __device__ __forceinline__ void dequant_row(const uint4 (&codes)[4], uint8_t* ti
                 const uint4 zp = *reinterpret_cast<const uint4*>(&sm.kz[8 * chunk]);
                 out = make_uint4(hfma2_u32(u[0], sc.x, zp.x), hfma2_u32(u[1], sc.y, zp.y), hfma2_u32(u[2], sc.z, zp.z),
                                  hfma2_u32(u[3], sc.w, zp.w));
+                if (other) out = make_uint4(hmul2_u32(out.x, o2), hmul2_u32(out.y, o2), hmul2_u32(out.z, o2), hmul2_u32(out.w, o2));
             } else {
                 out = make_uint4(hfma2_u32(u[0], s2, z2), hfma2_u32(u[1], s2, z2), hfma2_u32(u[2], s2, z2), hfma2_u32(u[3], s2, z2));
+                if (other) {
+                    const uint4 ot = *reinterpret_cast<const uint4*>(&sm.vo[8 * chunk]);
+                    out = make_uint4(hmul2_u32(out.x, ot.x), hmul2_u32(out.y, ot.y), hmul2_u32(out.z, ot.z), hmul2_u32(out.w, ot.w));
+                }
             }
             *reinterpret_cast<uint4*>(tile + tile_off(row, 8 * chunk)) = out;
         }
@@ -160,6 +173,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     const int t0 = static_cast<int>(static_cast<int64_t>(ntiles) * zs / P.ksplit);
     const int t1 = static_cast<int>(static_cast<int64_t>(ntiles) * (zs + 1) / P.ksplit);
     const int32_t* tbl = L.table();
+    const bool other = L.iters > 0;  // the cache carries balancing factors different from 1
     const uint32_t idesc_qk = tc::idesc_f16(kM, kN, false, false), idesc_pv = tc::idesc_f16(kM, D, false, true);
     const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v);
 
@@ -174,6 +188,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         uint4 codes[4], vcodes[4];
         uint32_t vsz;
         __half ks, kz;
+        __half ko, vo;  // balanced caches: other_K of this thread's key, other_V of this thread's dim
         int32_t page;  // page of this thread's key (-1: tile unusable)
         bool sealed, ok;
     };
@@ -196,6 +211,10 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         const __half* ksp = L.k_scale + page_head_offset(5, L.kv_heads, pg0, head);
         f.ks = ksp[(tid >> 1) * 5 + (tid & 1)];
         f.kz = ksp[(tid >> 1) * 5 + 2 + (tid & 1)];
+        if (other) {  // K scale row of a token ends with its other_K; V scale row d / 2 starts with other_V(d), other_V(d + 1)
+            f.ko = L.k_scale[page_head_offset(5, L.kv_heads, f.page, head) + (tid & 63) * 5 + 4];
+            f.vo = L.v_scale[page_head_offset(4, L.kv_heads, pg0, head) + (tid >> 1) * 4 + (tid & 1)];
+        }
     };
     KFetch cur, nxt;
     fetch_k(t0, nxt);
@@ -209,12 +228,13 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
             if (sealed) {
                 sm.ks[dim_slot(tid)] = cur.ks;
                 sm.kz[dim_slot(tid)] = cur.kz;
+                if (other) sm.vo[dim_slot(tid)] = cur.vo;
             }
             __syncthreads();  // scale tables visible
         }
         // ---- K tile -> shared memory (the previous P V does not touch the K buffer: P lives in tensor memory)
         if (sealed) {
-            dequant_row<true>(cur.codes, sm.k, tid, sm, 0, 0);
+            dequant_row<true>(cur.codes, sm.k, tid, sm, 0, 0, other, other ? __half_as_ushort(cur.ko) * 0x10001u : 0u);
         } else {
             stage_row_to_tile(L.stage_row(0, t & 1, head, tid), sm.k, tid, base + tid < kv_total);
         }
@@ -233,7 +253,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         }
         // ---- V tile -> shared memory (overlaps the QK MMA), then start fetching the next tile
         if (sealed) {
-            dequant_row<false>(cur.vcodes, sm.v, tid, sm, prmt(cur.vsz, cur.vsz, 0x1010), prmt(cur.vsz, cur.vsz, 0x3232));
+            dequant_row<false>(cur.vcodes, sm.v, tid, sm, prmt(cur.vsz, cur.vsz, 0x1010), prmt(cur.vsz, cur.vsz, 0x3232), other, 0u);
         } else {
             stage_row_to_tile(L.stage_row(1, t & 1, head, tid), sm.v, tid, base + tid < kv_total);
         }
@@ -315,6 +335,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         fence_proxy_async();
         tc::fence_before_sync();
         if (__syncthreads_or(failed)) { failed = true; break; }
+        if (other && nxt.ok && nxt.sealed) sm.vo[dim_slot(tid)] = nxt.vo;  // every thread is past this tile's V rows
         if (tid == 0) {
             tc::fence_after_sync();
 #pragma unroll
@@ -505,7 +526,7 @@ extern "C" int kvb_attn_prefill(const kvb_layer* layer, const void* q, const voi
     if (layer->stage == nullptr) return fail(KVB_EINVAL, "kvb_attn_prefill: layer has no stage buffer");
     if (tokens > 65535) return fail(KVB_ERANGE, "kvb_attn_prefill: %d tokens in one chunk (at most 65535)", tokens);
     if (int st = kvb_append(layer, k, v, positions_dev, tokens, stream)) return st;
-    if (layer->head_dim != 128 || layer->sinkhorn_iters != 0)  // shapes outside the tensor-core kernel: general kernel, same semantics
+    if (layer->head_dim != 128)  // two slices per key: general kernel, same semantics
         return launch_general_attention(layer, q, positions_dev, positions_dev + (tokens - 1), tokens, scale, kv_len_max, 0, INT_MAX,
                                         workspace, out, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
     return launch_chunk_attention(layer, q, positions_dev, tokens, scale, kv_len_max, workspace, out, static_cast<cudaStream_t>(stream),

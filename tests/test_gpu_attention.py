@@ -319,8 +319,9 @@ def _sync_cpu_from_gpu(tw):
 
 @pytest.mark.parametrize("D,H,QH,iters,T", [(256, 4, 24, 0, 700), (256, 2, 4, 0, 333), (128, 4, 24, 16, 600), (256, 2, 8, 16, 300)])
 def test_general_kernel_head_dim_256_and_sinkhorn(D, H, QH, iters, T):
-    """The reference engine's own geometry (head_dim 256, 16 Sinkhorn iterations) runs on the general kernel:
-    decode, a 4-row verify step and a small prefill chunk, against the oracle on the same cache bytes."""
+    """The reference engine's own geometry (head_dim 256, with and without Sinkhorn iterations) runs on the general
+    kernel, a balanced head_dim-128 cache on the tuned kernels: decode, a 4-row verify step and a small prefill chunk,
+    against the oracle on the same cache bytes."""
     import torch
 
     tw = Twin(D=D, H=H, QH=QH, capacity_tokens=T + 40, seed=101, iters=iters)
@@ -352,9 +353,77 @@ def test_general_kernel_head_dim_256_and_sinkhorn(D, H, QH, iters, T):
     tw.cpu.append(k[T + 4:], v[T + 4:], T + 4)
     _sync_cpu_from_gpu(tw)
     want = tw.cpu.attention(qc, pos, scale, QH, threads=4)
-    ok, msg = attn_close(out.float().cpu().numpy(), want)
+    from helpers import PREFILL_MAX_ABS, PREFILL_REL_L2
+    ok, msg = attn_close(out.float().cpu().numpy(), want, *((PREFILL_MAX_ABS, PREFILL_REL_L2) if D == 128 else ()))  # head_dim 128: tcgen05 kernel
     assert ok, "prefill: " + msg
     assert tw.gpu.errors() == 0
+
+
+@pytest.mark.parametrize("T", [1500, 5003])
+def test_balanced_cache_on_the_tuned_kernel(T):
+    """A head_dim-128 cache written with 16 Sinkhorn iterations (the engine's default) is read by the int8 decode
+    kernel with the per-key factor on the logits and the per-dim factor on the outputs: decode, verify steps of 2, 5
+    and 8 rows and a key-range partial, against the oracle over the very bytes the GPU wrote."""
+    import torch
+
+    from helpers import cpu_twin_of
+
+    H, QH, D = 4, 24, 128
+    tw = Twin(D=D, H=H, QH=QH, capacity_tokens=T + 16, seed=131, iters=16)
+    k, v = orc.synth_kv(132, T + 16, H, D, 1), orc.synth_kv(132, T + 16, H, D, 2)
+    tw.append(k[:T], v[:T])
+    scale = 1.0 / np.sqrt(D)
+    cpu = cpu_twin_of(tw.gpu)
+    q = orc.synth_q(132, 1, QH, D)
+    want = cpu.attention(q, [T - 1], scale, QH, threads=8, kv_total=T)
+    ok, msg = attn_close(_decode(tw, q[0], T - 1), want[0])
+    assert ok, "decode: " + msg
+    # a key range of the same cache as a partial, merged with the rest
+    cut = (T // 2) // 128 * 128
+    lib, capi = pkg().capi.load(), pkg().capi
+    import ctypes as C
+    qd = torch.from_numpy(q[0]).to(tw.dev)
+    pos = torch.tensor([T - 1], dtype=torch.int32, device=tw.dev)
+    pm = torch.empty((2, QH), dtype=torch.float32, device=tw.dev)
+    pl = torch.empty((2, QH), dtype=torch.float32, device=tw.dev)
+    po = torch.empty((2, QH, D), dtype=torch.float32, device=tw.dev)
+    ws = tw.gpu.workspace(T + 16, 1)
+    for i, (b, e) in enumerate(((0, cut), (cut, T))):
+        capi.check(lib.kvb_attn_decode_partial(C.byref(tw.gpu.c), C.c_void_p(qd.data_ptr()), C.c_void_p(pos.data_ptr()), scale, T + 16, b, e,
+                                               C.c_void_p(ws.data_ptr()), C.c_void_p(pm[i].data_ptr()), C.c_void_p(pl[i].data_ptr()),
+                                               C.c_void_p(po[i].data_ptr()), None))
+    out = pkg().merge_partials(pm, pl, po)
+    torch.cuda.synchronize()
+    ok, msg = attn_close(out.float().cpu().numpy(), want[0])
+    assert ok, "two key ranges merged: " + msg
+    # verify steps (appended rows stay in the stage, un-quantised)
+    done = T
+    for w in (2, 5, 8):
+        qw = orc.synth_q(133 + w, w, QH, D)
+        p = np.arange(done, done + w, dtype=np.int32)
+        out = tw.gpu.attn_verify(torch.from_numpy(qw).to(tw.dev), torch.from_numpy(k[done:done + w]).to(tw.dev),
+                                 torch.from_numpy(v[done:done + w]).to(tw.dev), torch.from_numpy(p).to(tw.dev), scale, T + 16)
+        torch.cuda.synchronize()
+        want_w = cpu_twin_of(tw.gpu).attention(qw, p, scale, QH, threads=8, kv_total=done + w)
+        from helpers import PREFILL_MAX_ABS, PREFILL_REL_L2
+        dense = w * (QH // H) >= 32  # the tcgen05 kernel rounds the de-quantised K and V to fp16
+        ok, msg = attn_close(out.float().cpu().numpy(), want_w, *((PREFILL_MAX_ABS, PREFILL_REL_L2) if dense else ()))
+        assert ok, f"verify of {w} rows: " + msg
+    # a chunk of 300 rows that completes tiles, on the tcgen05 kernel (factors applied while de-quantising)
+    done = T + 8
+    n = 300
+    k2, v2 = orc.synth_kv(140, n, H, D, 1), orc.synth_kv(140, n, H, D, 2)
+    tw2 = Twin(D=D, H=H, QH=QH, capacity_tokens=T + n + 16, seed=133, iters=16)
+    tw2.append(k[:T], v[:T])
+    qc = orc.synth_q(141, n, QH, D)
+    p = np.arange(T, T + n, dtype=np.int32)
+    out = tw2.gpu.attn_prefill(torch.from_numpy(qc).to(tw.dev), torch.from_numpy(k2).to(tw.dev), torch.from_numpy(v2).to(tw.dev),
+                               torch.from_numpy(p).to(tw.dev), scale, T + n + 16)
+    torch.cuda.synchronize()
+    want_c = cpu_twin_of(tw2.gpu).attention(qc, p, scale, QH, threads=8, kv_total=T + n)
+    ok, msg = attn_close(out.float().cpu().numpy(), want_c, PREFILL_MAX_ABS, PREFILL_REL_L2)
+    assert ok, "prefill chunk: " + msg
+    assert tw.gpu.errors() == 0 and tw2.gpu.errors() == 0
 
 
 def test_sharded_decode_ring_loopback_and_bounded_wait():
