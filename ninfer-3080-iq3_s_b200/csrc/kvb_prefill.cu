@@ -80,9 +80,9 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 // kPerDim: scale / zp pairs come from the per-dim tables (K); otherwise s2 / z2 hold the key's pair (V).
 // `other` (caches written with variance balancing): the result is multiplied by the key's other_K (K: o2, both halves)
 // or by the per-dim other_V table (V), reference kvarn128_codec.cuh:331-347; fp16 like the rest of this kernel.
-template <bool kPerDim>
+template <bool kPerDim, bool other>
 __device__ __forceinline__ void dequant_row(const uint4 (&codes)[4], uint8_t* tile, int row, const PrefillSmem& sm,
-                                            uint32_t s2, uint32_t z2, bool other, uint32_t o2) {
+                                            uint32_t s2, uint32_t z2, uint32_t o2) {
 #pragma unroll
     for (int v4 = 0; v4 < 4; ++v4) {
         const uint4 pk = codes[v4];
@@ -98,10 +98,10 @@ __device__ __forceinline__ void dequant_row(const uint4 (&codes)[4], uint8_t* ti
                 const uint4 zp = *reinterpret_cast<const uint4*>(&sm.kz[8 * chunk]);
                 out = make_uint4(hfma2_u32(u[0], sc.x, zp.x), hfma2_u32(u[1], sc.y, zp.y), hfma2_u32(u[2], sc.z, zp.z),
                                  hfma2_u32(u[3], sc.w, zp.w));
-                if (other) out = make_uint4(hmul2_u32(out.x, o2), hmul2_u32(out.y, o2), hmul2_u32(out.z, o2), hmul2_u32(out.w, o2));
+                if constexpr (other) out = make_uint4(hmul2_u32(out.x, o2), hmul2_u32(out.y, o2), hmul2_u32(out.z, o2), hmul2_u32(out.w, o2));
             } else {
                 out = make_uint4(hfma2_u32(u[0], s2, z2), hfma2_u32(u[1], s2, z2), hfma2_u32(u[2], s2, z2), hfma2_u32(u[3], s2, z2));
-                if (other) {
+                if constexpr (other) {
                     const uint4 ot = *reinterpret_cast<const uint4*>(&sm.vo[8 * chunk]);
                     out = make_uint4(hmul2_u32(out.x, ot.x), hmul2_u32(out.y, ot.y), hmul2_u32(out.z, ot.z), hmul2_u32(out.w, ot.w));
                 }
@@ -121,6 +121,8 @@ __device__ __forceinline__ void stage_row_to_tile(const __half* __restrict__ src
     }
 }
 
+// kOther: the cache carries balancing factors different from 1 (Sinkhorn iterations > 0).
+template <bool kOther>
 __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParams P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // the swizzled tiles need a 1024-byte aligned base; the launch reserves 1024 spare bytes for this
@@ -173,7 +175,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     const int t0 = static_cast<int>(static_cast<int64_t>(ntiles) * zs / P.ksplit);
     const int t1 = static_cast<int>(static_cast<int64_t>(ntiles) * (zs + 1) / P.ksplit);
     const int32_t* tbl = L.table();
-    const bool other = L.iters > 0;  // the cache carries balancing factors different from 1
+    constexpr bool other = kOther;
     const uint32_t idesc_qk = tc::idesc_f16(kM, kN, false, false), idesc_pv = tc::idesc_f16(kM, D, false, true);
     const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v);
 
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         const __half* ksp = L.k_scale + page_head_offset(5, L.kv_heads, pg0, head);
         f.ks = ksp[(tid >> 1) * 5 + (tid & 1)];
         f.kz = ksp[(tid >> 1) * 5 + 2 + (tid & 1)];
-        if (other) {  // K scale row of a token ends with its other_K; V scale row d / 2 starts with other_V(d), other_V(d + 1)
+        if constexpr (other) {  // K scale row of a token ends with its other_K; V scale row d / 2 starts with other_V(d), other_V(d + 1)
             f.ko = L.k_scale[page_head_offset(5, L.kv_heads, f.page, head) + (tid & 63) * 5 + 4];
             f.vo = L.v_scale[page_head_offset(4, L.kv_heads, pg0, head) + (tid >> 1) * 4 + (tid & 1)];
         }
@@ -228,13 +230,13 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
             if (sealed) {
                 sm.ks[dim_slot(tid)] = cur.ks;
                 sm.kz[dim_slot(tid)] = cur.kz;
-                if (other) sm.vo[dim_slot(tid)] = cur.vo;
+                if constexpr (other) sm.vo[dim_slot(tid)] = cur.vo;
             }
             __syncthreads();  // scale tables visible
         }
         // ---- K tile -> shared memory (the previous P V does not touch the K buffer: P lives in tensor memory)
         if (sealed) {
-            dequant_row<true>(cur.codes, sm.k, tid, sm, 0, 0, other, other ? __half_as_ushort(cur.ko) * 0x10001u : 0u);
+            dequant_row<true, other>(cur.codes, sm.k, tid, sm, 0, 0, other ? __half_as_ushort(cur.ko) * 0x10001u : 0u);
         } else {
             stage_row_to_tile(L.stage_row(0, t & 1, head, tid), sm.k, tid, base + tid < kv_total);
         }
@@ -253,7 +255,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         }
         // ---- V tile -> shared memory (overlaps the QK MMA), then start fetching the next tile
         if (sealed) {
-            dequant_row<false>(cur.vcodes, sm.v, tid, sm, prmt(cur.vsz, cur.vsz, 0x1010), prmt(cur.vsz, cur.vsz, 0x3232), other, 0u);
+            dequant_row<false, other>(cur.vcodes, sm.v, tid, sm, prmt(cur.vsz, cur.vsz, 0x1010), prmt(cur.vsz, cur.vsz, 0x3232), 0u);
         } else {
             stage_row_to_tile(L.stage_row(1, t & 1, head, tid), sm.v, tid, base + tid < kv_total);
         }
@@ -335,7 +337,9 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         fence_proxy_async();
         tc::fence_before_sync();
         if (__syncthreads_or(failed)) { failed = true; break; }
-        if (other && nxt.ok && nxt.sealed) sm.vo[dim_slot(tid)] = nxt.vo;  // every thread is past this tile's V rows
+        if constexpr (other) {
+            if (nxt.ok && nxt.sealed) sm.vo[dim_slot(tid)] = nxt.vo;  // every thread is past this tile's V rows
+        }
         if (tid == 0) {
             tc::fence_after_sync();
 #pragma unroll
@@ -504,9 +508,14 @@ int launch_chunk_attention(const kvb_layer* layer, const void* q, const int32_t*
     const int smem = static_cast<int>(sizeof(PrefillSmem)) + 1024;  // room to align the tiles to 1024 bytes
     static unsigned long long opted = 0;
     if (first_call_on_device(opted)) {
-        KVB_CUDA_OK(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        KVB_CUDA_OK(cudaFuncSetAttribute(prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        KVB_CUDA_OK(cudaFuncSetAttribute(prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     }
-    prefill_kernel<<<dim3(P.mtiles, layer->kv_heads, P.ksplit), kThreads, smem, s>>>(P);
+    if (layer->sinkhorn_iters > 0) {
+        prefill_kernel<true><<<dim3(P.mtiles, layer->kv_heads, P.ksplit), kThreads, smem, s>>>(P);
+    } else {
+        prefill_kernel<false><<<dim3(P.mtiles, layer->kv_heads, P.ksplit), kThreads, smem, s>>>(P);
+    }
     KVB_CUDA_OK(cudaGetLastError());
     const int total_rows = tokens * layer->q_heads;
     prefill_merge_kernel<<<total_rows, 256, 0, s>>>(P.ws_m, P.ws_l, P.ws_o, tokens, layer->q_heads, layer->kv_heads, P.mtiles,
