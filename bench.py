@@ -712,6 +712,7 @@ def measure_chunk_sharded(E, args):
            else torch.full((tokens,), n - 1, dtype=torch.int32, device=E.dev))
     out = torch.empty((tokens, QH, D), dtype=torch.float16, device=E.dev)
     chunk = sh.ShardedChunk(L, tokens)
+    ring_dec = None if prefill else sh.RingShardedDecode(L, sh.PeerRing.symmetric(QH, D, E.dev, tokens=8))
     kv_len_max = n + tokens + 8
     if tokens > 8:
         L.prefill_workspace(kv_len_max, tokens)
@@ -719,6 +720,12 @@ def measure_chunk_sharded(E, args):
         L.workspace(kv_len_max, tokens)
 
     def step():  # the drafts / the chunk are rolled back after every step: the same rows are appended at the same positions
+        if ring_dec is not None:  # verify step: partials exchanged over peer memory inside the reduce kernel
+            ring_dec.attn_verify(q, kv[:, :H], kv[:, H:], pos, E.scale, kv_len_max, out, owner=owner)
+        else:
+            chunk.attend(q, kv[:, :H], kv[:, H:], pos, E.scale, kv_len_max, out)
+
+    def step_nccl():
         chunk.attend(q, kv[:, :H], kv[:, H:], pos, E.scale, kv_len_max, out)
 
     def step_local():  # without the collective: append + partial only
@@ -734,14 +741,23 @@ def measure_chunk_sharded(E, args):
         for _ in range(3):
             step_local()
         ms_local = E.timed(step_local, args.steps)
+        ms_nccl = None
+        if ring_dec is not None:
+            for _ in range(3):
+                step_nccl()
+            ms_nccl = E.timed(step_nccl, args.steps)
     peak, peak_tf, kind = peaks()
     flops = 4.0 * QH * D * (tokens * ctx + tokens * (tokens + 1) / 2)
     tf = flops / (ms * 1e-3) / 1e12
     nbytes = decode_bytes(ctx)
     res = {"workload": (f"prefill chunk of 1,024 tokens over a {ctx}-token prefix" if prefill else "verify step of 8 rows over 131,072 tokens")
-                       + f", tile ranges on {E.world} GPUs: append on the owner, per-rank partials, one all-gather, merge",
+                       + f", tile ranges on {E.world} GPUs: append on the owner, per-rank partials, "
+                       + ("one all-gather, merge" if prefill else "exchange over peer memory inside the merge kernel"),
            "us": ms * 1e3, "us_without_collective": ms_local * 1e3, "collective_share": max(0.0, 1.0 - ms_local / ms),
            "bytes_gathered_per_rank": tokens * QH * (D + 2) * 4, "n_gpus": E.world, "clocks": clk.summary(), "error_words": L.errors()}
+    if ms_nccl is not None:
+        res["exchange"] = "peer stores + bounded polling inside reduce_kernel (kvb_attn_rows_sharded)"
+        res["us_with_nccl_all_gather_instead"] = ms_nccl * 1e3
     if prefill:
         res.update({"achieved": tf, "unit": "TFLOP/s", "frac": tf / (peak_tf * E.world), "peak": peak_tf, "peak_kind": kind + " (sustained bf16, per GPU)", "bound": "tensor"})
     else:

@@ -185,10 +185,22 @@ typedef struct kvb_peer_ring {
     uint32_t* state;
     int32_t rank, world;
     uint32_t max_spins;
+    uint32_t rows;  /* query rows (tokens x q heads) the ring buffers hold: they were sized with
+                       kvb_peer_ring_bytes(world, rows, head_dim); 0 = the layer's q_heads (one token per call) */
 } kvb_peer_ring;
 size_t kvb_peer_ring_bytes(int world, int q_heads, int head_dim);
 int kvb_attn_decode_sharded(const kvb_layer* layer, const void* q, const int32_t* pos_dev, float scale, int kv_len_max,
                             void* workspace, const kvb_peer_ring* ring, void* out, void* stream);
+
+/* The same exchange for a verify step of 1..8 query tokens over a range-sharded sequence: causal attention of the
+ * `rows` tokens (q: [rows][q_heads][head_dim], the same on every rank) over THIS rank's cache, partials pushed to
+ * the peers and merged inside the reduce kernel, the finished rows in `out` on every rank.  positions_dev[rows] are
+ * positions in this cache's own coordinates: on the rank that owns the open tile -- which has appended the rows
+ * with kvb_append before this call -- the rows' own positions, on the other ranks their last position, repeated.
+ * The ring buffers must hold rows * q_heads query rows (kvb_peer_ring.rows).  No counterpart in the reference
+ * (single GPU); the single-GPU operator is causal_attention_small_t_launch (P3:3508-3545). */
+int kvb_attn_rows_sharded(const kvb_layer* layer, const void* q, const int32_t* positions_dev, int rows, float scale,
+                          int kv_len_max, void* workspace, const kvb_peer_ring* ring, void* out, void* stream);
 
 /* One decode step: append the token at *pos_dev (k, v: [kv_heads][head_dim]), then decode attention of q over the
  * cache including it -- kvb_append followed by kvb_attn_decode (ring == NULL) or kvb_attn_decode_sharded (ring given:

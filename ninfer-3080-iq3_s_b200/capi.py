@@ -34,7 +34,7 @@ class kvb_layer(C.Structure):
 
 class kvb_peer_ring(C.Structure):
     _fields_ = [("peer_bufs", C.POINTER(C.c_void_p)), ("local_buf", C.c_void_p), ("state", C.c_void_p), ("rank", C.c_int32),
-                ("world", C.c_int32), ("max_spins", C.c_uint32)]
+                ("world", C.c_int32), ("max_spins", C.c_uint32), ("rows", C.c_uint32)]
 
 
 # name -> (restype, argtypes); every symbol the header declares
@@ -65,6 +65,8 @@ SYMBOLS = {
     "kvb_peer_ring_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "kvb_attn_decode_sharded": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p,
                                           C.POINTER(kvb_peer_ring), C.c_void_p, C.c_void_p]),
+    "kvb_attn_rows_sharded": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_void_p,
+                                        C.POINTER(kvb_peer_ring), C.c_void_p, C.c_void_p]),
     "kvb_append_decode": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_void_p,
                                     C.POINTER(kvb_peer_ring), C.c_void_p, C.c_void_p]),
     "kvb_attn_verify": (C.c_int, [C.POINTER(kvb_layer), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,

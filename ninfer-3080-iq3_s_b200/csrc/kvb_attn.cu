@@ -1410,9 +1410,13 @@ extern "C" size_t kvb_peer_ring_bytes(int world, int q_heads, int head_dim) {
 
 namespace kvb {
 // Checks a ring descriptor and turns it into the kernel's form.
-static int make_push_target(const kvb_layer* layer, const kvb_peer_ring* ring, const void* out, const char* who, PushTarget& push) {
+static int make_push_target(const kvb_layer* layer, const kvb_peer_ring* ring, const void* out, const char* who, PushTarget& push,
+                            int tokens = 1) {
     if (ring == nullptr || ring->peer_bufs == nullptr || ring->local_buf == nullptr || ring->state == nullptr || out == nullptr)
         return fail(KVB_EINVAL, "%s: null ring / buffers / out", who);
+    if (layer != nullptr && static_cast<uint32_t>(tokens * layer->q_heads) > (ring->rows ? ring->rows : static_cast<uint32_t>(layer->q_heads)))
+        return fail(KVB_ERANGE, "%s: %d query rows, the ring buffers hold %u", who, tokens * layer->q_heads,
+                    ring->rows ? ring->rows : static_cast<uint32_t>(layer->q_heads));
     if (ring->world < 1 || ring->world > kRingMaxWorld || ring->rank < 0 || ring->rank >= ring->world)
         return fail(KVB_EINVAL, "%s: rank %d of world %d (1..%d ranks)", who, ring->rank, ring->world, kRingMaxWorld);
     push = PushTarget{};
@@ -1439,6 +1443,17 @@ extern "C" int kvb_attn_decode_sharded(const kvb_layer* layer, const void* q, co
     if (int st = make_push_target(layer, ring, out, "kvb_attn_decode_sharded", push)) return st;
     return launch_attention(layer, q, pos_dev, pos_dev, 1, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr, nullptr, nullptr,
                             static_cast<cudaStream_t>(stream), "kvb_attn_decode_sharded", &push);
+}
+
+extern "C" int kvb_attn_rows_sharded(const kvb_layer* layer, const void* q, const int32_t* positions_dev, int rows, float scale,
+                                     int kv_len_max, void* workspace, const kvb_peer_ring* ring, void* out, void* stream) {
+    using namespace kvb;
+    if (rows < 1 || rows > 8) return fail(KVB_ERANGE, "kvb_attn_rows_sharded: %d query tokens (1..8)", rows);
+    if (positions_dev == nullptr) return fail(KVB_EINVAL, "kvb_attn_rows_sharded: null positions");
+    PushTarget push{};
+    if (int st = make_push_target(layer, ring, out, "kvb_attn_rows_sharded", push, rows)) return st;
+    return launch_attention(layer, q, positions_dev, positions_dev + (rows - 1), rows, scale, kv_len_max, 0, INT_MAX, workspace, out, nullptr,
+                            nullptr, nullptr, static_cast<cudaStream_t>(stream), "kvb_attn_rows_sharded", &push);
 }
 
 // One decode step of a sequence in one call: append the newest token, then attend (kvb_append followed by

@@ -153,4 +153,25 @@ inline void causal_attention_cached_small_t_sharded_launch(const void* q, const 
                   "causal_attention_cached_small_t_sharded");
 }
 
+// A verify step of `width` (1..8) rows over such a sequence: the rank that owns the open tile appends the rows
+// first (k, v non-null there, null elsewhere), every rank attends its own range, the partials are exchanged by the
+// kernels (the ring buffers must hold width * q_heads rows: kvb_peer_ring::rows).
+inline void causal_attention_small_t_sharded_launch(const void* q, const void* k, const void* v, const std::int32_t* local_pos,
+                                                    int width, float scale, const Kvarn128LayerView& view, const kvb_peer_ring& ring,
+                                                    void* workspace, void* out, cudaStream_t stream) {
+    if (k != nullptr && v != nullptr)
+        detail::raise(kvb_append(&view.layer, k, v, local_pos, width, stream), "causal_attention_small_t_sharded (append)");
+    detail::raise(kvb_attn_rows_sharded(&view.layer, q, local_pos, width, scale, view.kv_len_max, workspace, &ring, out, stream),
+                  "causal_attention_small_t_sharded");
+}
+
+// One decode step as one call: append the token at *pos, then attend (ring: null, or the ring of a sharded sequence on
+// the rank that owns the open tile).
+inline void kv_cache_append_then_decode_launch(const void* q, const void* k, const void* v, const std::int32_t* pos, float scale,
+                                               const Kvarn128LayerView& view, const kvb_peer_ring* ring, void* workspace, void* out,
+                                               cudaStream_t stream) {
+    detail::raise(kvb_append_decode(&view.layer, q, k, v, pos, scale, view.kv_len_max, workspace, ring, out, stream),
+                  "kv_cache_append_then_decode");
+}
+
 }  // namespace ninfer::ops

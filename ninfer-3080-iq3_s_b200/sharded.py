@@ -128,7 +128,7 @@ class PeerRing:
     `PeerRing.symmetric(...)` allocates it with torch's symmetric memory over the process group (NVLink peer
     mappings); `PeerRing.loopback(...)` builds a single-process stand-in whose "peers" are local buffers (tests)."""
 
-    def __init__(self, local_buf, peer_ptrs, rank: int, world: int, device, max_spins: int = 0, keep=()):
+    def __init__(self, local_buf, peer_ptrs, rank: int, world: int, device, max_spins: int = 0, keep=(), rows: int = 0):
         import ctypes as C
 
         import torch
@@ -139,7 +139,7 @@ class PeerRing:
         self.peer_ptrs = (C.c_void_p * world)(*[int(p) for p in peer_ptrs])
         self.state = torch.zeros(4, dtype=torch.int32, device=device)
         self.c = capi.kvb_peer_ring(peer_bufs=self.peer_ptrs, local_buf=local_buf.data_ptr(),
-                                    state=self.state.data_ptr(), rank=rank, world=world, max_spins=max_spins)
+                                    state=self.state.data_ptr(), rank=rank, world=world, max_spins=max_spins, rows=rows)
         self._C = C
 
     @staticmethod
@@ -149,26 +149,27 @@ class PeerRing:
         return capi.load().kvb_peer_ring_bytes(world, q_heads, head_dim)
 
     @classmethod
-    def symmetric(cls, q_heads: int, head_dim: int, device, group=None, max_spins: int = 0):
+    def symmetric(cls, q_heads: int, head_dim: int, device, group=None, max_spins: int = 0, tokens: int = 1):
+        """`tokens`: query tokens per call the ring must hold (1 = decode only, 8 = verify steps too)."""
         import torch
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
 
         group = group or dist.group.WORLD
         world, rank = dist.get_world_size(group), dist.get_rank(group)
-        buf = symm_mem.empty(cls.nbytes(world, q_heads, head_dim) // 4, dtype=torch.float32, device=device)
+        buf = symm_mem.empty(cls.nbytes(world, tokens * q_heads, head_dim) // 4, dtype=torch.float32, device=device)
         buf.zero_()
         hdl = symm_mem.rendezvous(buf, group)
         torch.cuda.synchronize()
         dist.barrier(group)  # every rank's buffer is zeroed before anybody may push
-        return cls(buf, [int(p) for p in hdl.buffer_ptrs], rank, world, device, max_spins, keep=(hdl,))
+        return cls(buf, [int(p) for p in hdl.buffer_ptrs], rank, world, device, max_spins, keep=(hdl,), rows=tokens * q_heads)
 
     @classmethod
-    def loopback(cls, q_heads: int, head_dim: int, device, world: int = 1, rank: int = 0, max_spins: int = 0):
+    def loopback(cls, q_heads: int, head_dim: int, device, world: int = 1, rank: int = 0, max_spins: int = 0, tokens: int = 1):
         import torch
 
-        bufs = [torch.zeros(cls.nbytes(world, q_heads, head_dim) // 4, dtype=torch.float32, device=device) for _ in range(world)]
-        return cls(bufs[rank], [b.data_ptr() for b in bufs], rank, world, device, max_spins, keep=tuple(bufs))
+        bufs = [torch.zeros(cls.nbytes(world, tokens * q_heads, head_dim) // 4, dtype=torch.float32, device=device) for _ in range(world)]
+        return cls(bufs[rank], [b.data_ptr() for b in bufs], rank, world, device, max_spins, keep=tuple(bufs), rows=tokens * q_heads)
 
 
 class RingShardedDecode:
@@ -189,4 +190,24 @@ class RingShardedDecode:
                                                        local_len_max, C.c_void_p(L.workspace(local_len_max, 1).data_ptr()),
                                                        C.byref(self.ring.c), C.c_void_p(out.data_ptr()),
                                                        C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out
+
+    def attn_verify(self, q, k, v, local_positions, scale: float, local_len_max: int, out, owner: bool):
+        """A verify step of 1..8 rows: the owner of the open tile appends the rows (k, v), every rank attends its own
+        range and the reduce kernel exchanges the partials over the ring (kvb_attn_rows_sharded): three launches on
+        the owner, two elsewhere, no collective.  local_positions as for ShardedChunk.attend."""
+        import ctypes as C
+
+        import torch
+
+        from . import capi
+
+        L = self.layer
+        rows = int(q.shape[0])
+        if owner:
+            L.append(k, v, local_positions)
+        capi.check(capi.load().kvb_attn_rows_sharded(C.byref(L.c), C.c_void_p(q.data_ptr()), C.c_void_p(local_positions.data_ptr()), rows,
+                                                     scale, local_len_max, C.c_void_p(L.workspace(local_len_max, rows).data_ptr()),
+                                                     C.byref(self.ring.c), C.c_void_p(out.data_ptr()),
+                                                     C.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return out

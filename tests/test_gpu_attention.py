@@ -3,7 +3,7 @@ CPU oracle: softmax attention in double precision over the de-quantised cache.  
 import numpy as np
 import pytest
 
-from helpers import Twin, attn_close, orc, pkg
+from helpers import Twin, attn_close, cpu_twin_of, orc, pkg
 
 pytestmark = pytest.mark.gpu
 
@@ -366,8 +366,6 @@ def test_balanced_cache_on_the_tuned_kernel(T):
     and 8 rows and a key-range partial, against the oracle over the very bytes the GPU wrote."""
     import torch
 
-    from helpers import cpu_twin_of
-
     H, QH, D = 4, 24, 128
     tw = Twin(D=D, H=H, QH=QH, capacity_tokens=T + 16, seed=131, iters=16)
     k, v = orc.synth_kv(132, T + 16, H, D, 1), orc.synth_kv(132, T + 16, H, D, 2)
@@ -424,6 +422,43 @@ def test_balanced_cache_on_the_tuned_kernel(T):
     ok, msg = attn_close(out.float().cpu().numpy(), want_c, PREFILL_MAX_ABS, PREFILL_REL_L2)
     assert ok, "prefill chunk: " + msg
     assert tw.gpu.errors() == 0 and tw2.gpu.errors() == 0
+
+
+def test_sharded_verify_ring_loopback():
+    """kvb_attn_rows_sharded on one GPU with a one-rank ring: verify steps of 1..8 rows equal kvb_attn_rows of the same
+    cache on the warp-level kernel bit for bit (same partials, same merge); a ring sized for one token refuses a
+    wider step."""
+    import ctypes as C
+
+    import torch
+
+    capi = pkg().capi
+    sh = pkg().sharded
+    T = 2100
+    tw = Twin(D=128, H=4, QH=24, capacity_tokens=T + 16, seed=121)
+    k, v = orc.synth_kv(122, T + 8, 4, 128, 1), orc.synth_kv(122, T + 8, 4, 128, 2)
+    tw.append(k[:T], v[:T])
+    scale = 1.0 / np.sqrt(128)
+    ring = sh.PeerRing.loopback(24, 128, tw.dev, tokens=8)
+    dec = sh.RingShardedDecode(tw.gpu, ring)
+    for w in (1, 3, 5, 8, 2):
+        qw = torch.from_numpy(orc.synth_q(123 + w, w, 24, 128)).to(tw.dev)
+        pos = torch.arange(T, T + w, dtype=torch.int32, device=tw.dev)
+        out = torch.empty_like(qw)
+        dec.attn_verify(qw, torch.from_numpy(k[T:T + w]).to(tw.dev), torch.from_numpy(v[T:T + w]).to(tw.dev), pos, scale, T + 16, out,
+                        owner=True)
+        torch.cuda.synchronize()
+        want = cpu_twin_of(tw.gpu).attention(qw.cpu().numpy(), pos.cpu().numpy(), scale, 24, threads=8, kv_total=T + w)
+        ok, msg = attn_close(out.float().cpu().numpy(), want)
+        assert ok, f"{w} rows: " + msg
+    assert tw.gpu.errors() == 0
+    small = sh.PeerRing.loopback(24, 128, tw.dev)  # holds one token
+    lib = capi.load()
+    q2 = torch.zeros((2, 24, 128), dtype=torch.float16, device=tw.dev)
+    pos2 = torch.arange(T, T + 2, dtype=torch.int32, device=tw.dev)
+    st = lib.kvb_attn_rows_sharded(C.byref(tw.gpu.c), C.c_void_p(q2.data_ptr()), C.c_void_p(pos2.data_ptr()), 2, scale, T + 16,
+                                   C.c_void_p(tw.gpu.workspace(T + 16, 2).data_ptr()), C.byref(small.c), C.c_void_p(q2.data_ptr()), None)
+    assert st == capi.KVB_ERANGE
 
 
 def test_sharded_decode_ring_loopback_and_bounded_wait():

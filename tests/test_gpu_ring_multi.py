@@ -52,6 +52,7 @@ def _worker(rank, world, port, T, ret):
         scale = 1.0 / np.sqrt(D)
 
         def filled(n_tokens, k_rows, v_rows, seed, room):
+            room += 16  # the verify steps below
             lp = (n_tokens + room + 63) // 64 + 2
             lp += lp & 1
             L = p.KvarnLayer(D, H, QH, lp, torch.from_numpy(orc.shuffled_table(seed, lp, lp)), device=str(dev))
@@ -94,6 +95,27 @@ def _worker(rank, world, port, T, ret):
             worst = max(worst, float((out.float() - ref.float()).abs().max()))
         assert local.errors() == 0 and full.errors() == 0
         assert int(ring.state[0].item()) == steps
+        dist.barrier()
+        # ---- verify steps of 3 and 8 rows over the sharded sequence, partials exchanged by the reduce kernel (a ring that
+        #      holds eight tokens); against the single-GPU verify of the unsharded cache.  The rows are rolled back after
+        #      each step (the same positions are written again).
+        ring8 = sh.PeerRing.symmetric(QH, D, dev, tokens=8)
+        dec8 = sh.RingShardedDecode(local, ring8)
+        base_full, base_local = T + steps, n + steps
+        kx, vx = orc.synth_kv(91, 8, H, D, 1), orc.synth_kv(91, 8, H, D, 2)
+        for w in (3, 8):
+            qw = torch.from_numpy(orc.synth_q(92 + w, w, QH, D)).to(dev)
+            kw, vw = torch.from_numpy(kx[:w]).to(dev), torch.from_numpy(vx[:w]).to(dev)
+            gpos = torch.arange(base_full, base_full + w, dtype=torch.int32, device=dev)
+            lpos = (torch.arange(base_local, base_local + w, dtype=torch.int32, device=dev) if owner
+                    else torch.full((w,), n - 1, dtype=torch.int32, device=dev))
+            out_w = torch.empty((w, QH, D), dtype=torch.float16, device=dev)
+            dec8.attn_verify(qw, kw, vw, lpos, scale, n + steps + 16, out_w, owner=owner)
+            ref_w = full.attn_verify(qw, kw, vw, gpos, scale, T + steps + 16)
+            torch.cuda.synchronize()
+            ok, msg = attn_close(out_w.float().cpu().numpy(), ref_w.float().cpu().numpy().astype(np.float64), 2.0 ** -8, 5e-3)
+            assert ok, f"rank {rank} verify of {w} rows vs the single-GPU verify: {msg}"
+        assert local.errors() == 0 and full.errors() == 0
         dist.barrier()
         # ---- a peer that never launches: rank 0 calls on a fresh ring with a short wait, rank 1 skips the call
         ring2 = sh.PeerRing.symmetric(QH, D, dev, max_spins=2000)
