@@ -65,6 +65,7 @@ struct AttnParams {
     int T;
     float scale_log2;    // softmax scale * log2(e)
     int nsplit;          // CTAs over the sealed tiles of a head; the last one also reads the open tile
+    int block_rows;      // GQA-merged query rows per row block (grid z): 8 (one 8-row block per warp) or 16 (two)
     int key_begin, key_end;
     float* ws_m;         // [H][Z][nsplit][16]
     float* ws_l;
@@ -360,7 +361,7 @@ __device__ __forceinline__ void attn_cta(const AttnParams& P, int split, int hea
         qpos[i] = -1;
         const int r = warp + W * i;
         if (r < 8 * NB) {
-            const int Rr = zb * kRows + r, tq = Rr / G, gq = Rr % G;
+            const int Rr = zb * P.block_rows + r, tq = Rr / G, gq = Rr % G;
             if (tq < P.T) {
                 const uint16_t* qrow = P.q + (static_cast<int64_t>(tq) * L.q_heads + head * G + gq) * D;
 #pragma unroll
@@ -942,6 +943,7 @@ __global__ void __launch_bounds__(W * 32, 1) attn_batch_kernel(const BatchParams
     P.T = 1;
     P.scale_log2 = B.scale_log2;
     P.nsplit = B.plan.prefix[b + 1] - B.plan.prefix[b];
+    P.block_rows = kRows;
     P.key_begin = 0;
     P.key_end = INT_MAX;
     P.ws_m = B.ws_m;
@@ -988,7 +990,7 @@ __device__ __forceinline__ bool ring_arrived(const uint4& w, uint32_t call) { re
 
 __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
                                                                   const float* __restrict__ ws_o, int parts, int T, int q_heads,
-                                                                  int kv_heads, int zblocks, int dtype, uint16_t* __restrict__ out,
+                                                                  int kv_heads, int zblocks, int block_rows, int dtype, uint16_t* __restrict__ out,
                                                                   float* __restrict__ part_m, float* __restrict__ part_l,
                                                                   float* __restrict__ part_o, const PushTarget push,
                                                                   const BatchPlan plan) {
@@ -1001,7 +1003,7 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
         parts = plan.prefix[tq + 1] - plan.prefix[tq];
         base = (static_cast<int64_t>(head) * plan.prefix[plan.n] + plan.prefix[tq]) * kRows + gq;
     } else {
-        const int R = tq * G + gq, zb = R / kRows, r = R % kRows;
+        const int R = tq * G + gq, zb = R / block_rows, r = R % block_rows;
         base = (static_cast<int64_t>(head) * zblocks + zb) * parts * kRows + r;
     }
     grid_dependency_wait();  // launched while the attention kernel still runs: its partials are complete from here on
@@ -1202,7 +1204,7 @@ __global__ void __launch_bounds__(128) merge_kernel(const float* __restrict__ pm
 
 int sm_count() { return device_sm_count(); }
 
-int zblocks_of(int q_heads, int kv_heads, int rows) { return (rows * (q_heads / kv_heads) + kRows - 1) / kRows; }
+int zblocks_of(int q_heads, int kv_heads, int rows, int block_rows) { return (rows * (q_heads / kv_heads) + block_rows - 1) / block_rows; }
 
 // Splits over the sealed tiles of a head: one CTA per SM in total, no more splits than tiles.
 int split_count(int kv_len_max, int kv_heads, int zblocks) {
@@ -1245,18 +1247,42 @@ cudaError_t launch_attn(dim3 grid, cudaStream_t stream, const AttnParams& P) {
 // pages needs ceil(n / W) rounds; a round and the fixed part (set-up, merge of the warps) take longer the more warps
 // share the SM.  Times in microseconds, fitted to sweeps over 32K .. 379K tokens on B200: with 8 warps the SM is
 // not yet saturated (a round of 8 pages takes 2.5 us, one of 16 pages 3.9 us).
-int decode_warps(int kv_len_max, int nsplit) {
+int decode_warps(int kv_len_max, int nsplit, float* cost_us = nullptr) {
     static const int forced = [] { const char* e = std::getenv("KVB_DECODE_WARPS"); return e ? std::atoi(e) : 0; }();
-    if (forced == 8 || forced == 12 || forced == 16) return forced;
     static const struct { int warps; float fixed_us, round_us; } kChoice[3] = {{16, 8.8f, 3.93f}, {12, 7.3f, 2.98f}, {8, 6.1f, 2.52f}};
     const int pages = 2 * (kv_len_max / kTile), per_cta = (pages + nsplit - 1) / nsplit;
     int best = 16;
     float best_cost = 1e30f;
     for (const auto& c : kChoice) {
+        if ((forced == 8 || forced == 12 || forced == 16) && c.warps != forced) continue;
         const float cost = c.fixed_us + static_cast<float>((per_cta + c.warps - 1) / c.warps) * c.round_us;
         if (cost < best_cost - 1e-3f) { best_cost = cost; best = c.warps; }
     }
+    if (cost_us != nullptr) *cost_us = best_cost;
     return best;
+}
+
+// How a call with `T` query tokens is cut into row blocks (grid z).  Up to 8 merged rows: one block.  More: either
+// blocks of 16 rows on the two-block kernel (8 warps of 255 registers: about 4.4 us per round of 8 pages, measured at
+// 131,072 tokens) or blocks of 8 rows on the one-block kernel with its 8 / 12 / 16 warps (more CTAs per head, so fewer
+// key splits and more pages per CTA, but up to twice the warps): whichever the cost model puts first.  Balanced
+// caches have the one-block kernel with 8 warps only, and take the 16-row blocks.
+struct RowPlan {
+    int nb, warps, block_rows, zblocks, nsplit;
+};
+RowPlan plan_rows(int kv_len_max, int kv_heads, int q_heads, int T, bool balanced) {
+    const int merged = T * (q_heads / kv_heads);
+    RowPlan one{1, 16, 8, zblocks_of(q_heads, kv_heads, T, 8), 0};
+    one.nsplit = split_count(kv_len_max, kv_heads, one.zblocks);
+    float cost_one = 0.0f;
+    one.warps = decode_warps(kv_len_max, one.nsplit, &cost_one);
+    if (balanced) one.warps = 8;
+    if (merged <= 8) return one;
+    RowPlan two{2, kWarpsWide, 16, zblocks_of(q_heads, kv_heads, T, 16), 0};
+    two.nsplit = split_count(kv_len_max, kv_heads, two.zblocks);
+    const int pages = 2 * (kv_len_max / kTile), per_cta = (pages + two.nsplit - 1) / two.nsplit;
+    const float cost_two = 6.1f + static_cast<float>((per_cta + kWarpsWide - 1) / kWarpsWide) * 4.4f;
+    return balanced || cost_two <= cost_one ? two : one;
 }
 
 int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_dev, const int32_t* total_pos_dev, int T,
@@ -1273,8 +1299,8 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     if (layer->head_dim != 128)  // two slices per key: general kernel, same semantics
         return launch_general_attention(layer, q, pos_dev, total_pos_dev, T, scale, kv_len_max, key_begin, key_end, workspace, out,
                                         part_m, part_l, part_o, stream);
-    const int Z = zblocks_of(layer->q_heads, layer->kv_heads, T);
-    const int nsplit = split_count(kv_len_max, layer->kv_heads, Z);
+    const RowPlan plan = plan_rows(kv_len_max, layer->kv_heads, layer->q_heads, T, layer->sinkhorn_iters != 0);
+    const int Z = plan.zblocks, nsplit = plan.nsplit;
     const int parts = nsplit;
     AttnParams P;
     P.L = make_view(*layer);
@@ -1284,13 +1310,14 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     P.T = T;
     P.scale_log2 = scale * 1.4426950408889634f;
     P.nsplit = nsplit;
+    P.block_rows = plan.block_rows;
     P.key_begin = key_begin;
     P.key_end = key_end;
     const size_t rows = static_cast<size_t>(layer->kv_heads) * Z * parts * kRows;
     P.ws_m = static_cast<float*>(workspace);
     P.ws_l = P.ws_m + rows;
     P.ws_o = P.ws_l + rows;
-    const bool upper = T * (layer->q_heads / layer->kv_heads) > 8;
+    const bool upper = plan.nb == 2;
     const dim3 grid(parts, layer->kv_heads, Z);
     if (layer->sinkhorn_iters != 0) {  // balanced caches: other_K per key, other_V per dim (more registers: 8 warps)
         if (upper) {
@@ -1301,7 +1328,7 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     } else if (upper) {
         KVB_CUDA_OK((launch_attn<2, kWarpsWide>(grid, stream, P)));
     } else {
-        switch (decode_warps(kv_len_max, nsplit)) {
+        switch (plan.warps) {
             case 8: KVB_CUDA_OK((launch_attn<1, 8>(grid, stream, P))); break;
             case 12: KVB_CUDA_OK((launch_attn<1, 12>(grid, stream, P))); break;
             default: KVB_CUDA_OK((launch_attn<1, 16>(grid, stream, P))); break;
@@ -1309,7 +1336,7 @@ int launch_attention(const kvb_layer* layer, const void* q, const int32_t* pos_d
     }
     const int total_rows = T * layer->q_heads;
     KVB_CUDA_OK(launch_early(reduce_kernel, dim3(total_rows), dim3(kReduceWarps * 32), 0, stream, P.ws_m, P.ws_l, P.ws_o, parts, T,
-                             layer->q_heads, layer->kv_heads, Z, layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o,
+                             layer->q_heads, layer->kv_heads, Z, plan.block_rows, layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o,
                              push != nullptr ? *push : PushTarget{}, BatchPlan{}));
     return KVB_OK;
 }
@@ -1323,14 +1350,17 @@ static constexpr int kDenseRows = 32;
 extern "C" int kvb_split_capacity(int kv_len_max, int kv_heads, int q_heads, int rows, int batch) {
     (void)batch;
     if (kv_heads < 1 || q_heads < kv_heads || rows < 1) return 0;
-    return kvb::split_count(kv_len_max, kv_heads, kvb::zblocks_of(q_heads, kv_heads, rows));
+    return kvb::plan_rows(kv_len_max, kv_heads, q_heads, rows > 8 ? 8 : rows, false).nsplit;
 }
 
 // Bytes one call with `r` query tokens needs (the split count, hence the size, is not monotonic in r).
 static size_t workspace_bytes_for_rows(int kv_len_max, int kv_heads, int q_heads, int head_dim, int r) {
-    const int Z = kvb::zblocks_of(q_heads, kv_heads, r);
-    const size_t parts = kvb::split_count(kv_len_max, kv_heads, Z);
-    size_t bytes = static_cast<size_t>(kv_heads) * Z * parts * kvb::kRows * (head_dim + 2) * sizeof(float);
+    size_t bytes = 0;
+    for (int block_rows = 8; block_rows <= 16; block_rows += 8) {  // either cut of the rows into blocks (plan_rows)
+        const int Z = kvb::zblocks_of(q_heads, kv_heads, r, block_rows);
+        const size_t parts = kvb::split_count(kv_len_max, kv_heads, Z);
+        bytes = std::max(bytes, static_cast<size_t>(kv_heads) * Z * parts * kvb::kRows * (head_dim + 2) * sizeof(float));
+    }
     const size_t general = kvb::general_workspace_bytes(kv_len_max, q_heads, head_dim, r);
     if (general > bytes) bytes = general;
     if (r * (q_heads / kv_heads) >= kDenseRows) {  // verify steps this wide run on the chunk-attention kernel
@@ -1548,7 +1578,7 @@ extern "C" int kvb_attn_decode_batch(const kvb_layer* layers_dev, int batch, int
     if (q_heads / kv_heads > 8) KVB_CUDA_OK(launch_early(attn_batch_kernel<2, kWarpsWide>, dim3(total, kv_heads, 1), dim3(kWarpsWide * 32), smem2, st, B));
     else KVB_CUDA_OK(launch_early(attn_batch_kernel<1, kWarpsDecode>, dim3(total, kv_heads, 1), dim3(kWarpsDecode * 32), smem1, st, B));
     KVB_CUDA_OK(launch_early(reduce_kernel, dim3(batch * q_heads), dim3(kReduceWarps * 32), 0, st, B.ws_m, B.ws_l, B.ws_o, 0, batch, q_heads,
-                             kv_heads, 1, dtype, static_cast<uint16_t*>(out), static_cast<float*>(nullptr), static_cast<float*>(nullptr),
+                             kv_heads, 1, kRows, dtype, static_cast<uint16_t*>(out), static_cast<float*>(nullptr), static_cast<float*>(nullptr),
                              static_cast<float*>(nullptr), PushTarget{}, B.plan));
     return KVB_OK;
 }
