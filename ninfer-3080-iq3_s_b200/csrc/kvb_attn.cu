@@ -1071,14 +1071,22 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
         const unsigned long long* in = push.local_buf + static_cast<int64_t>(slot) * push.world * block;
         const uint32_t everyone = (push.world >= 32 ? 0xffffffffu : (1u << push.world) - 1u) & ~(1u << push.rank);
         uint32_t spins = 0;
-        // (m, l) of every rank
+        // (m, l) of every rank and, in the same polling rounds, the o words of the first kRingGroup ranks (all of them up
+        // to eight GPUs): one memory latency after the last word has landed, not one per kind of word
         float rm[kRingMaxWorld], rl[kRingMaxWorld];
-        uint32_t pending = everyone;
-        while (pending != 0u && spins < push.max_spins) {
+        uint4 a0[kRingGroup], b0[kRingGroup];
+        uint32_t pending = everyone, pending_o = everyone & ((1u << kRingGroup) - 1u);
+        while ((pending | pending_o) != 0u && spins < push.max_spins) {
             uint4 w[kRingMaxWorld];
 #pragma unroll
             for (int p = 0; p < kRingMaxWorld; ++p)
                 if (pending >> p & 1u) w[p] = ring_load2(in + p * block + ml_off);
+#pragma unroll
+            for (int i = 0; i < kRingGroup; ++i)
+                if (pending_o >> i & 1u) {
+                    a0[i] = ring_load2(in + i * block + o_off);
+                    b0[i] = ring_load2(in + i * block + o_off + 2);
+                }
 #pragma unroll
             for (int p = 0; p < kRingMaxWorld; ++p)
                 if ((pending >> p & 1u) && ring_arrived(w[p], call)) {
@@ -1086,9 +1094,12 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
                     rl[p] = __uint_as_float(w[p].z);
                     pending &= ~(1u << p);
                 }
-            if (pending != 0u) { ++spins; __nanosleep(32); }
+#pragma unroll
+            for (int i = 0; i < kRingGroup; ++i)
+                if ((pending_o >> i & 1u) && ring_arrived(a0[i], call) && ring_arrived(b0[i], call)) pending_o &= ~(1u << i);
+            if ((pending | pending_o) != 0u) { ++spins; __nanosleep(32); }
         }
-        bool ok = pending == 0u;
+        bool ok = (pending | pending_o) == 0u;
         float gm = mine;
 #pragma unroll
         for (int p = 0; p < kRingMaxWorld; ++p)
@@ -1099,7 +1110,11 @@ __global__ void __launch_bounds__(kReduceWarps * 32) reduce_kernel(const float* 
         for (int g = 0; g < kRingMaxWorld; g += kRingGroup) {
             if (g >= push.world || !ok) continue;
             uint4 a[kRingGroup], b[kRingGroup];
-            pending = everyone >> g & ((1u << kRingGroup) - 1u);
+            pending = g == 0 ? 0u : everyone >> g & ((1u << kRingGroup) - 1u);  // the first group is already here
+            if (g == 0) {
+#pragma unroll
+                for (int i = 0; i < kRingGroup; ++i) { a[i] = a0[i]; b[i] = b0[i]; }
+            }
             while (pending != 0u && spins < push.max_spins) {
 #pragma unroll
                 for (int i = 0; i < kRingGroup; ++i)
