@@ -43,12 +43,16 @@ __host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool a_mn_major, 
            (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]; one thread issues.  K = 16 per instruction for 16-bit operands.
+// D[tmem] (+)= A[smem] * B[smem].  K = 16 per instruction for 16-bit operands.  Called by a whole, converged warp with
+// warp-uniform operands: one elected lane issues the instruction (always the same lane, so a later commit by the
+// same election covers it); keeping the operand arithmetic warp-uniform lets it run on the uniform datapath, where
+// the instruction takes its operands from.
 __device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
         : "memory");
 }
@@ -56,15 +60,21 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uin
 // two elements per 32-bit column (even k in the low half), 8 columns per instruction.
 __device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
         : "memory");
 }
-// All MMAs issued so far by this thread arrive on `bar` when they have completed (implies the before-sync fence).
+// All MMAs issued so far by the elected lane of this (whole, converged) warp arrive on `bar` when they have completed
+// (implies the before-sync fence).
 __device__ __forceinline__ void commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar))
+        : "memory");
 }
 
 // ---- TMEM <-> registers: lane = 32 * (warp % 4) + lane id, 32 consecutive 32-bit columns ---------------------
