@@ -1527,12 +1527,28 @@ static_assert(sizeof(LayerView) == sizeof(kvb_layer) && offsetof(LayerView, erro
               "the device reads kvb_layer structs as LayerView");
 
 // Parts (splits over the sealed tiles; the last one also reads the open tile) of every sequence from the host's
-// bounds of their lengths: about eight CTAs per SM in total, at least 8 tiles per split, at most 64 splits per sequence.
+// bounds of their lengths: chunks of at least 8 tiles, at most 64 splits per sequence.  The chunk size trades the fixed
+// part of a CTA (about 8.8 us with 16 warps: set-up, first fetch, merge) against the balance of the SMs: the candidates
+// are 2 .. 12 CTAs per SM in total, costed as (CTAs x time of a CTA) / SMs + half a CTA for the ragged end, a CTA taking
+// 8.8 us + 3.93 us per round of 16 pages (the same figures as the single-sequence decode).
 int plan_batch(const int32_t* kv_len_max, int batch, int kv_heads, BatchPlan& plan) {
     int64_t total_tiles = 0;
     for (int b = 0; b < batch; ++b) total_tiles += kv_len_max[b] / kTile;
-    const int64_t want = std::max<int64_t>(batch, static_cast<int64_t>(8) * sm_count() / kv_heads);
-    const int64_t chunk = std::max<int64_t>(8, (total_tiles + want - 1) / want);
+    const int sms = sm_count();
+    int64_t chunk = 8;
+    float best = 1e30f;
+    static const int kPerSm[] = {2, 3, 4, 6, 8, 12};
+    for (int per_sm : kPerSm) {
+        const int64_t want = std::max<int64_t>(batch, static_cast<int64_t>(per_sm) * sms / kv_heads);
+        const int64_t c = std::max<int64_t>(8, (total_tiles + want - 1) / want);
+        int64_t ctas = 0;
+        for (int b = 0; b < batch; ++b)
+            ctas += std::min<int64_t>(std::max<int64_t>((kv_len_max[b] / kTile + c - 1) / c, 1), kReduceWarps * kMaxPartsPerWarp);
+        ctas *= kv_heads;
+        const float one = 8.8f + 3.93f * static_cast<float>((2 * c + kWarpsDecode - 1) / kWarpsDecode);
+        const float cost = static_cast<float>(ctas) * one / static_cast<float>(sms) + 0.5f * one;
+        if (cost < best) { best = cost; chunk = c; }
+    }
     plan.n = batch;
     plan.prefix[0] = 0;
     for (int b = 0; b < batch; ++b) {
