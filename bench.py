@@ -34,11 +34,11 @@ sys.path.insert(0, ROOT)
 
 D, H, QH, LAYERS = 128, 4, 24, 16
 LONG_CTX = 378944
-# DRAM bytes (read + write) one decode call moves per token of context, from an ncu capture of attn_kernel at 131,072
-# tokens (74.57 MB read + 1.33 MB written): the codes and axes the kernel fetches (the second page's copy of the per-dim
-# scales is skipped) plus the partials written; traffic grows in proportion to the context (same pages per token, same
-# splits per SM).
-TRAFFIC_BYTES_PER_TOKEN = 579.1
+# DRAM bytes (read + write) one decode call moves per token of context, from ncu captures of attn_kernel: 213.92 MB
+# read + 4.73 MB written at 378,944 tokens (581.6 B per token at 131,072): the codes and axes the kernel fetches (the
+# second page's copy of the per-dim scales is skipped) plus the partials written; traffic grows in proportion to the
+# context (same pages per token, same splits per SM).
+TRAFFIC_BYTES_PER_TOKEN = 577.0
 SEALED_B, TAIL_B = 140, 512  # algorithmic bytes per sealed / open-tile token per KV head (codes + 12 B of axes | fp16 K+V rows)
 
 
