@@ -80,9 +80,10 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 // kPerDim: scale / zp pairs come from the per-dim tables (K); otherwise s2 / z2 hold the key's pair (V).
 // `other` (caches written with variance balancing): the result is multiplied by the key's other_K (K: o2, both halves)
 // or by the per-dim other_V table (V), reference kvarn128_codec.cuh:331-347; fp16 like the rest of this kernel.
+// ks / kz / vo: the per-dim tables of the tile in shared memory (tile dim order).
 template <bool kPerDim, bool other>
-__device__ __forceinline__ void dequant_row(const uint4 (&codes)[4], uint8_t* tile, int row, const PrefillSmem& sm,
-                                            uint32_t s2, uint32_t z2, uint32_t o2) {
+__device__ __forceinline__ void dequant_row(const uint4 (&codes)[4], uint8_t* tile, int row, const __half* ks, const __half* kz,
+                                            const __half* vo, uint32_t s2, uint32_t z2, uint32_t o2) {
 #pragma unroll
     for (int v4 = 0; v4 < 4; ++v4) {
         const uint4 pk = codes[v4];
@@ -94,15 +95,15 @@ __device__ __forceinline__ void dequant_row(const uint4 (&codes)[4], uint8_t* ti
             unpack8(w[i], u);
             uint4 out;
             if constexpr (kPerDim) {
-                const uint4 sc = *reinterpret_cast<const uint4*>(&sm.ks[8 * chunk]);
-                const uint4 zp = *reinterpret_cast<const uint4*>(&sm.kz[8 * chunk]);
+                const uint4 sc = *reinterpret_cast<const uint4*>(&ks[8 * chunk]);
+                const uint4 zp = *reinterpret_cast<const uint4*>(&kz[8 * chunk]);
                 out = make_uint4(hfma2_u32(u[0], sc.x, zp.x), hfma2_u32(u[1], sc.y, zp.y), hfma2_u32(u[2], sc.z, zp.z),
                                  hfma2_u32(u[3], sc.w, zp.w));
                 if constexpr (other) out = make_uint4(hmul2_u32(out.x, o2), hmul2_u32(out.y, o2), hmul2_u32(out.z, o2), hmul2_u32(out.w, o2));
             } else {
                 out = make_uint4(hfma2_u32(u[0], s2, z2), hfma2_u32(u[1], s2, z2), hfma2_u32(u[2], s2, z2), hfma2_u32(u[3], s2, z2));
                 if constexpr (other) {
-                    const uint4 ot = *reinterpret_cast<const uint4*>(&sm.vo[8 * chunk]);
+                    const uint4 ot = *reinterpret_cast<const uint4*>(&vo[8 * chunk]);
                     out = make_uint4(hmul2_u32(out.x, ot.x), hmul2_u32(out.y, ot.y), hmul2_u32(out.z, ot.z), hmul2_u32(out.w, ot.w));
                 }
             }
@@ -118,6 +119,43 @@ __device__ __forceinline__ void stage_row_to_tile(const __half* __restrict__ src
         uint4 r = live ? reinterpret_cast<const uint4*>(src)[chunk] : make_uint4(0, 0, 0, 0);
         *reinterpret_cast<uint4*>(tile + tile_off(row, 8 * chunk)) =
             make_uint4(prmt(r.x, r.z, 0x5410), prmt(r.x, r.z, 0x7632), prmt(r.y, r.w, 0x5410), prmt(r.y, r.w, 0x7632));
+    }
+}
+
+// The Q tile of a CTA: rows (token, q head of this KV head) `first_row` .. + 127 rotated, scaled, rounded to fp16 and
+// stored in tile dim order; rows beyond the chunk are zeros.  One warp per row, lane l holds dims l + 32 j; the rows of
+// a warp are taken eight at a time with every global load issued before the first rotation (a row per iteration cost
+// one memory latency each: 32 us per CTA with four warps).
+__device__ __forceinline__ void build_q_tile(const PrefillParams& P, const LayerView& L, int first_row, int head, int G, uint8_t* q_tile,
+                                             int* row_pos, int warp, int lane) {
+    constexpr int kWarps = kThreads / 32, kBatch = 8;
+    for (int j0 = 0; j0 < kM / kWarps; j0 += kBatch) {
+        uint16_t raw[kBatch][4];
+        int rp[kBatch];
+#pragma unroll
+        for (int jj = 0; jj < kBatch; ++jj) {
+            const int r = warp + kWarps * (j0 + jj), R = first_row + r, tq = R / G, gq = R % G;
+            rp[jj] = -1;
+            raw[jj][0] = raw[jj][1] = raw[jj][2] = raw[jj][3] = 0;
+            if (tq < P.T) {
+                const uint16_t* qrow = P.q + (static_cast<int64_t>(tq) * L.q_heads + head * G + gq) * D;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) raw[jj][j] = qrow[lane + 32 * j];
+                rp[jj] = P.pos[tq];
+            }
+        }
+#pragma unroll
+        for (int jj = 0; jj < kBatch; ++jj) {
+            const int r = warp + kWarps * (j0 + jj);
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = L.dtype == KVB_DTYPE_BF16 ? in_to_f32<true>(raw[jj][j]) : in_to_f32<false>(raw[jj][j]);
+            if (rp[jj] >= 0) hadamard_warp<D>(v, lane);  // warp-uniform: a row is real or not for the whole warp
+            if (lane == 0) row_pos[r] = rp[jj];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<__half*>(q_tile + tile_off(r, dim_slot(lane + 32 * j))) = __float2half_rn(v[j] * P.scale_log2);
+        }
     }
 }
 
@@ -140,24 +178,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         mbar_fence_init();
         sm.flags[0] = 0;
     }
-    // ---- Q tile: rotate, scale, fp16, tile dim order.  One warp per row, lane l holds dims l + 32 j.
-    for (int r = warp; r < kM; r += kThreads / 32) {
-        const int R = mt * kM + r, tq = R / G, gq = R % G;
-        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        int rp = -1;
-        if (tq < P.T) {
-            const uint16_t* qrow = P.q + (static_cast<int64_t>(tq) * L.q_heads + head * G + gq) * D;
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                v[j] = L.dtype == KVB_DTYPE_BF16 ? in_to_f32<true>(qrow[lane + 32 * j]) : in_to_f32<false>(qrow[lane + 32 * j]);
-            hadamard_warp<D>(v, lane);
-            rp = P.pos[tq];
-        }
-        if (lane == 0) sm.row_pos[r] = rp;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<__half*>(sm.q + tile_off(r, dim_slot(lane + 32 * j))) = __float2half_rn(v[j] * P.scale_log2);
-    }
+    build_q_tile(P, L, mt * kM, head, G, sm.q, sm.row_pos, warp, lane);
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
@@ -249,7 +270,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         }
         // ---- K tile -> shared memory (the previous P V does not touch the K buffer: P lives in tensor memory)
         if (sealed) {
-            dequant_row<true, other>(cur.codes, sm.k, tid, sm, 0, 0, other ? __half_as_ushort(cur.ko) * 0x10001u : 0u);
+            dequant_row<true, other>(cur.codes, sm.k, tid, sm.ks, sm.kz, sm.vo, 0, 0, other ? __half_as_ushort(cur.ko) * 0x10001u : 0u);
         } else {
             stage_row_to_tile(L.stage_row(0, t & 1, head, tid), sm.k, tid, base + tid < kv_total);
         }
@@ -268,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
         }
         // ---- V tile -> shared memory (overlaps the QK MMA), then start fetching the next tile
         if (sealed) {
-            dequant_row<false, other>(cur.vcodes, sm.v, tid, sm, prmt(cur.vsz, cur.vsz, 0x1010), prmt(cur.vsz, cur.vsz, 0x3232), 0u);
+            dequant_row<false, other>(cur.vcodes, sm.v, tid, sm.ks, sm.kz, sm.vo, prmt(cur.vsz, cur.vsz, 0x1010), prmt(cur.vsz, cur.vsz, 0x3232), 0u);
         } else {
             stage_row_to_tile(L.stage_row(1, t & 1, head, tid), sm.v, tid, base + tid < kv_total);
         }
@@ -396,61 +417,373 @@ __global__ void __launch_bounds__(kThreads, 2) prefill_kernel(const PrefillParam
     if (warp == 0) tc::tmem_dealloc(sm.tmem_base, kTmemCols);
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// verify_kernel: the same attention for a verify step (at most 64 GQA-merged rows: 8 tokens x 8 query heads per KV
+// head), with the two halves of the CTA given different work.  Only TMEM lanes 0-63 hold rows, so only warps 0 and 1
+// have a softmax to do; in prefill_kernel warps 2 and 3 idle through it and every warp de-quantises a quarter of
+// each tile in between.  Here
+//   warps 2, 3   de-quantise: K(t+1) into the K buffer as soon as S(t) = Q K(t)^T has completed -- while warps 0, 1
+//                are busy with the softmax of step t -- and V(t+1) as soon as P V(t) has completed; thread = one key
+//                row of each page of the tile; codes fetched a tile ahead;
+//   warps 0, 1   softmax of their rows; warp 0 also issues the MMAs (one elected lane): Q K^T when the K tile is
+//                ready, P V when both warps have stored P and the V tile is ready.
+// The chain of a step shrinks from de-quantise + issue + softmax + issue to issue + softmax + issue.  Hand-offs are
+// mbarriers (bounded waits that also watch a CTA-wide abort flag); the two warps of a half meet at a named barrier
+// once per step, and a warp whose wait gave up still goes to that barrier before it leaves, so nobody is left waiting.
+struct __align__(1024) VerifySmem {
+    uint8_t q[kTileBytes];
+    uint8_t k[kTileBytes];
+    uint8_t v[kTileBytes];
+    __half ks[2][D], kz[2][D], vo[2][D];  // per-dim tables of the tile, by step parity
+    uint64_t bar_s, bar_o, k_ready, v_ready;
+    uint32_t tmem_base;
+    int row_pos[kM];
+    int abort_flag, bad_tile;
+};
+
+__device__ __forceinline__ bool verify_wait(uint64_t* bar, uint32_t parity, VerifySmem& sm) {
+    bool ok = false;
+    for (uint32_t i = 0; i < kSpinLimit && !ok; ++i) {
+        ok = mbar_try_wait(bar, parity);
+        if (!ok && *reinterpret_cast<volatile int*>(&sm.abort_flag) != 0) break;
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) *reinterpret_cast<volatile int*>(&sm.abort_flag) = 1;
+    return ok;
+}
+
+template <bool kOther>
+__global__ void __launch_bounds__(kThreads, 2) verify_kernel(const PrefillParams P) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    VerifySmem& sm = *reinterpret_cast<VerifySmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
+    const LayerView& L = P.L;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int head = blockIdx.y, zs = blockIdx.z;
+    const int G = L.q_heads / L.kv_heads;
+    const int kv_total = *P.total_pos + 1;
+
+    if (warp == 0) tc::tmem_alloc(&sm.tmem_base, kTmemCols);
+    if (tid == 0) {
+        mbar_init(&sm.bar_s, 1);
+        mbar_init(&sm.bar_o, 1);
+        mbar_init(&sm.k_ready, 2);  // lane 0 of each de-quantising warp
+        mbar_init(&sm.v_ready, 2);
+        mbar_fence_init();
+        sm.abort_flag = 0;
+        sm.bad_tile = 0;
+    }
+    build_q_tile(P, L, 0, head, G, sm.q, sm.row_pos, warp, lane);  // rows beyond the step's are zeros; the MMA reads all 128
+    fence_proxy_async();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_s = sm.tmem_base, tmem_o = sm.tmem_base + kN;
+    int max_pos = -1, min_pos = INT_MAX;
+    for (int r = 0; r < 64; ++r) {
+        const int p = sm.row_pos[r];
+        if (p >= 0) { max_pos = max(max_pos, p); min_pos = min(min_pos, p); }
+    }
+    const int ntiles = max_pos < 0 ? 0 : min((kv_total + kN - 1) / kN, max_pos / kN + 1);
+    const int t0 = static_cast<int>(static_cast<int64_t>(ntiles) * zs / P.ksplit);
+    const int t1 = static_cast<int>(static_cast<int64_t>(ntiles) * (zs + 1) / P.ksplit);
+    const int n = t1 - t0;
+    bool failed = false;
+    volatile int* abort_flag = &sm.abort_flag;
+
+    if (warp >= 2) {
+        // =========================== de-quantise ===========================
+        const int dt = tid - 64;  // key rows dt of both pages of the tile (tile rows dt and dt + 64); dims dt and dt + 64
+        const int32_t* tbl = L.table();
+        struct Fetch {
+            uint4 codes[2][4], vcodes[2][4];
+            uint32_t vsz[2];
+            __half ks[2], kz[2], ko[2], vo[2];
+            bool bad;
+        };
+        int32_t ids_a = -1, ids_b = -1;  // pages of the tile the next fetch asks for, looked up a step earlier
+        auto sealed_tile = [&](int t) { return t * kN + kN <= kv_total; };
+        auto lookup = [&](int t) {
+            ids_a = ids_b = -1;
+            if (t < t1 && sealed_tile(t)) {
+                ids_a = L.page_of(tbl, 2 * t);
+                ids_b = L.page_of(tbl, 2 * t + 1);
+            }
+        };
+        auto fetch = [&](int t, Fetch& f) {
+            int32_t pg[2] = {ids_a, ids_b};
+            lookup(t + 1);
+            f.bad = false;
+            if (t >= t1 || !sealed_tile(t)) return;
+            if (pg[0] < 0 || pg[1] < 0) { f.bad = true; pg[0] = pg[1] = 0; }  // reported in the error word; the tile is masked
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint4* kc = reinterpret_cast<const uint4*>(L.k_code + page_head_offset(64, L.kv_heads, pg[h], head) + dt * 64);
+                const uint4* vc = reinterpret_cast<const uint4*>(L.v_code + page_head_offset(64, L.kv_heads, pg[h], head) + dt * 64);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    f.codes[h][i] = kc[i];
+                    f.vcodes[h][i] = vc[i];
+                }
+                f.vsz[h] = *reinterpret_cast<const uint32_t*>(L.v_scale + page_head_offset(4, L.kv_heads, pg[h], head) + dt * 4 + 2);
+                // per-dim entries of the tile (stored in both pages): this thread's dims are dt and dt + 64
+                const int d = dt + 64 * h;
+                const __half* ksp = L.k_scale + page_head_offset(5, L.kv_heads, pg[0], head);
+                f.ks[h] = ksp[(d >> 1) * 5 + (d & 1)];
+                f.kz[h] = ksp[(d >> 1) * 5 + 2 + (d & 1)];
+                if constexpr (kOther) {
+                    f.ko[h] = L.k_scale[page_head_offset(5, L.kv_heads, pg[h], head) + dt * 5 + 4];
+                    f.vo[h] = L.v_scale[page_head_offset(4, L.kv_heads, pg[0], head) + (d >> 1) * 4 + (d & 1)];
+                }
+            }
+        };
+        Fetch cur, nxt;
+        if (n > 0) {
+            lookup(t0);
+            fetch(t0, nxt);
+        }
+        for (int i = 0; i < n; ++i) {
+            const int t = t0 + i, base = t * kN, par = i & 1;
+            const bool sealed = sealed_tile(t);
+            cur = nxt;
+            // ---- K: the buffer (and the tables of this parity) are free once S(i-1) has completed
+            if (!failed && i > 0 && !verify_wait(&sm.bar_s, (i - 1) & 1, sm)) failed = true;
+            if (!failed && sealed) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    sm.ks[par][dim_slot(dt + 64 * h)] = cur.ks[h];
+                    sm.kz[par][dim_slot(dt + 64 * h)] = cur.kz[h];
+                    if constexpr (kOther) sm.vo[par][dim_slot(dt + 64 * h)] = cur.vo[h];
+                }
+                if (dt == 0 && cur.bad) sm.bad_tile = 1;  // sticky: the error word is set, the result is void anyway
+            }
+            named_barrier_sync(2, 64);  // tables visible to both warps; a warp that gave up meets its partner here
+            if (*abort_flag) break;
+            if (sealed) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    dequant_row<true, kOther>(cur.codes[h], sm.k, dt + 64 * h, sm.ks[par], sm.kz[par], sm.vo[par], 0, 0,
+                                              kOther ? __half_as_ushort(cur.ko[h]) * 0x10001u : 0u);
+            } else {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    stage_row_to_tile(L.stage_row(0, t & 1, head, dt + 64 * h), sm.k, dt + 64 * h, base + dt + 64 * h < kv_total);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.k_ready);
+            fetch(t + 1, nxt);
+            // ---- V: the buffer is free once P V(i-1) has completed
+            if (i > 0 && !verify_wait(&sm.bar_o, (i - 1) & 1, sm)) { failed = true; continue; }
+            if (sealed) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    dequant_row<false, kOther>(cur.vcodes[h], sm.v, dt + 64 * h, sm.ks[par], sm.kz[par], sm.vo[par],
+                                               prmt(cur.vsz[h], cur.vsz[h], 0x1010), prmt(cur.vsz[h], cur.vsz[h], 0x3232), 0u);
+            } else {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    stage_row_to_tile(L.stage_row(1, t & 1, head, dt + 64 * h), sm.v, dt + 64 * h, base + dt + 64 * h < kv_total);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.v_ready);
+        }
+    } else {
+        // =========================== softmax (warps 0, 1) and MMA issue (warp 0) ===========================
+        const uint32_t lane_base = static_cast<uint32_t>(32 * warp) << 16;
+        const int my_pos = sm.row_pos[tid];
+        const bool warp_has_rows = __any_sync(0xffffffffu, my_pos >= 0);
+        const uint32_t idesc_qk = tc::idesc_f16(kM, kN, false, false), idesc_pv = tc::idesc_f16(kM, D, false, true);
+        const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v);
+        float m_run = -INFINITY, l_run = 0.0f;
+        for (int i = 0; i < n; ++i) {
+            const int base = (t0 + i) * kN;
+            const bool sealed = base + kN <= kv_total;
+            if (warp == 0 && !failed) {  // S(i) = Q K(i)^T: the K tile is ready; P V(i-1), which reads P from the columns of S, has completed
+                if (!verify_wait(&sm.k_ready, i & 1, sm) || (i > 0 && !verify_wait(&sm.bar_o, (i - 1) & 1, sm))) {
+                    failed = true;
+                } else {
+                    tc::fence_after_sync();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk) {
+                        const uint32_t o = (kk >> 2) * 16384 + (kk & 3) * 32;
+                        tc::mma_f16_ss(tmem_s, tc::smem_desc(q_addr + o, 16, 1024), tc::smem_desc(k_addr + o, 16, 1024), idesc_qk, kk > 0);
+                    }
+                    tc::commit(&sm.bar_s);
+                }
+            }
+            if (!failed && !verify_wait(&sm.bar_s, i & 1, sm)) failed = true;
+            tc::fence_after_sync();
+            if (!failed && warp_has_rows) {
+                const bool all_masked = *reinterpret_cast<volatile int*>(&sm.bad_tile) != 0;
+                float s[kN];
+                {
+                    uint32_t r0[32], r1[32], r2[32], r3[32];
+                    tc::tmem_ld32(tmem_s + lane_base, r0);
+                    tc::tmem_ld32(tmem_s + lane_base + 32, r1);
+                    tc::tmem_ld32(tmem_s + lane_base + 64, r2);
+                    tc::tmem_ld32(tmem_s + lane_base + 96, r3);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        s[j] = __uint_as_float(r0[j]);
+                        s[32 + j] = __uint_as_float(r1[j]);
+                        s[64 + j] = __uint_as_float(r2[j]);
+                        s[96 + j] = __uint_as_float(r3[j]);
+                    }
+                }
+                if (base + kN - 1 > min_pos || !sealed || all_masked) {
+#pragma unroll
+                    for (int j = 0; j < kN; ++j)
+                        if (base + j > my_pos || base + j >= kv_total || all_masked) s[j] = -INFINITY;
+                }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int j = 0; j < kN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                constexpr float kLazy = 8.0f;  // lazy reference point, as in prefill_kernel
+                const bool grown = mx > m_run + kLazy || (m_run == -INFINITY && mx > -INFINITY);
+                const float m_new = grown ? mx : m_run;
+                const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+                const float alpha = grown ? fast_exp2(m_run - m_use) : 1.0f;
+                const bool moved = i > 0 && grown;
+                m_run = m_new;
+                float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float p0 = fast_exp2(s[64 * c + 2 * j] - m_use), p1 = fast_exp2(s[64 * c + 2 * j + 1] - m_use);
+                        sum4[j & 3] += p0 + p1;
+                        pk[j] = pack_half2(p0, p1);
+                    }
+                    tc::tmem_st32(tmem_s + lane_base + 32 * c, pk);
+                }
+                tc::tmem_st_wait();
+                l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+                if (__any_sync(0xffffffffu, moved)) {  // P V(i-1) completed before S(i) was issued: O may be rescaled
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        tc::tmem_ld32(tmem_o + lane_base + 32 * c, r);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+                        tc::tmem_st32(tmem_o + lane_base + 32 * c, r);
+                    }
+                    tc::tmem_st_wait();
+                }
+            }
+            tc::fence_before_sync();
+            named_barrier_sync(1, 64);  // P of both warps is in tensor memory; a warp that gave up meets its partner here
+            if (*abort_flag) { failed = true; break; }
+            if (warp == 0) {  // O += P V(i)
+                if (!verify_wait(&sm.v_ready, i & 1, sm)) {
+                    failed = true;
+                } else {
+                    tc::fence_after_sync();
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)
+                        tc::mma_f16_ts(tmem_o, tmem_s + 8 * kk, tc::smem_desc(v_addr + kk * 2048, 16384, 1024), idesc_pv, i > 0 || kk > 0);
+                    tc::commit(&sm.bar_o);
+                }
+            }
+        }
+        // ---- partial of this key range: m (log2 units), l, o in tile dim order
+        if (n > 0 && !failed && !verify_wait(&sm.bar_o, (n - 1) & 1, sm)) failed = true;
+        if (*abort_flag) failed = true;
+        tc::fence_after_sync();
+        const bool have = n > 0 && !failed;
+        const int64_t idx = (static_cast<int64_t>(head) * P.ksplit + zs) * kM + tid;
+        if (my_pos >= 0) {
+            P.ws_m[idx] = have ? m_run : -INFINITY;
+            P.ws_l[idx] = have ? l_run : 0.0f;
+        }
+        float* orow = P.ws_o + idx * D;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if (!warp_has_rows) break;
+            uint32_t r[32];
+            if (have) {
+                tc::tmem_ld32(tmem_o + lane_base + 32 * c, r);
+                tc::tmem_ld_wait();
+            }
+            if (my_pos < 0) continue;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(orow + 32 * c + j) =
+                    have ? make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]))
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    if ((failed || *abort_flag) && lane == 0) L.flag(KVB_ERR_WAIT_TIMEOUT);
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(sm.tmem_base, kTmemCols);
+}
+
 // Merge the key ranges of one query row, normalise, undo the tile dim order, rotate back, store -- or, for a cache
 // that holds only a range of the sequence, export the merged partial instead (m in natural-log units, l, o in the
 // rotated domain and natural dim order, not normalised).
 // One CTA of 8 warps per row: warp w takes ranges w, w+8, ..; lane l owns dims l + 32 j.  The loop is pure load
 // latency, so it is unrolled to keep several ranges in flight; the warp sums meet in shared memory.
+template <int kPer>  // ranges per warp: ksplit <= 8 kPer
 __global__ void __launch_bounds__(256) prefill_merge_kernel(const float* __restrict__ ws_m, const float* __restrict__ ws_l,
                                                             const float* __restrict__ ws_o, int T, int q_heads, int kv_heads,
                                                             int mtiles, int ksplit, int dtype, uint16_t* __restrict__ out,
                                                             float* __restrict__ part_m, float* __restrict__ part_l,
                                                             float* __restrict__ part_o) {
     __shared__ float so[8][D];
-    __shared__ float sl[8];
+    __shared__ float sl[8], smx[8];
     const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = q_heads / kv_heads, tq = row / q_heads, qh = row % q_heads, head = qh / G, R = tq * G + qh % G;
     const int64_t base = ((static_cast<int64_t>(head) * mtiles + R / kM) * ksplit) * kM + R % kM;
-    float m = -INFINITY;
-    for (int z = lane; z < ksplit; z += 32) m = fmaxf(m, ws_m[base + static_cast<int64_t>(z) * kM]);
+    // Warp w merges ranges w, w + 8, .. (kPer of them; at most 16: ksplit <= 128) relative to their own maximum, every
+    // load issued before the first use: one trip to memory for the whole row; the eight warp results meet in shared
+    // memory.  kPer is a template parameter so that a chunk (a few ranges, tens of thousands of rows) keeps the
+    // registers low and the occupancy high.
+    float pm[kPer], pl[kPer], po[kPer][4];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    for (int k = 0; k < kPer; ++k) {
+        const int z = warp + 8 * k;
+        const bool on = z < ksplit;
+        const int64_t i = base + static_cast<int64_t>(on ? z : 0) * kM;
+        pm[k] = on ? ws_m[i] : -INFINITY;
+        pl[k] = on ? ws_l[i] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) po[k][j] = on ? ws_o[i * D + dim_slot(lane + 32 * j)] : 0.0f;
+    }
+    float mw = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < kPer; ++k) mw = fmaxf(mw, pm[k]);
     float l = 0.0f, o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    if (m != -INFINITY) {
-        for (int z0 = warp; z0 < ksplit; z0 += 64) {  // eight ranges of the warp at a time, every load issued before the first use
-            float pm[8], pl[8], po[8][4];
+    if (mw != -INFINITY) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const int z = z0 + 8 * k;
-                const bool on = z < ksplit;
-                const int64_t i = base + static_cast<int64_t>(on ? z : z0) * kM;
-                pm[k] = on ? ws_m[i] : -INFINITY;
-                pl[k] = ws_l[i];
+        for (int k = 0; k < kPer; ++k) {
+            const float w = fast_exp2(pm[k] - mw);  // 0 for a range that is not there
+            l += w * pl[k];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) po[k][j] = ws_o[i * D + dim_slot(lane + 32 * j)];
-            }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                const float w = fast_exp2(pm[k] - m);  // 0 for a range that is not there
-                l += w * pl[k];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) o[j] += w * po[k][j];
-            }
+            for (int j = 0; j < 4; ++j) o[j] += w * po[k][j];
         }
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) so[warp][lane + 32 * j] = o[j];
-    if (lane == 0) sl[warp] = l;
+    if (lane == 0) { sl[warp] = l; smx[warp] = mw; }
     __syncthreads();
     if (warp != 0) return;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) m = fmaxf(m, smx[w]);
     l = 0.0f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[j] = 0.0f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) {
-        l += sl[w];
+        const float wt = smx[w] == -INFINITY ? 0.0f : fast_exp2(smx[w] - m);
+        l += wt * sl[w];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) o[j] += so[w][lane + 32 * j];
+        for (int j = 0; j < 4; ++j) o[j] += wt * so[w][lane + 32 * j];
     }
     if (part_m != nullptr) {
         if (lane == 0) { part_m[row] = m * 0.6931471805599453f; part_l[row] = l; }
@@ -525,15 +858,30 @@ int launch_chunk_attention(const kvb_layer* layer, const void* q, const int32_t*
         KVB_CUDA_OK(cudaFuncSetAttribute(prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         KVB_CUDA_OK(cudaFuncSetAttribute(prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     }
-    if (layer->sinkhorn_iters > 0) {
+    const bool few_rows = tokens * (layer->q_heads / layer->kv_heads) <= 64;  // a verify step: the role-split kernel
+    if (few_rows) {
+        const int vsmem = static_cast<int>(sizeof(VerifySmem)) + 1024;
+        static unsigned long long vopted = 0;
+        if (first_call_on_device(vopted)) {
+            KVB_CUDA_OK(cudaFuncSetAttribute(verify_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, vsmem));
+            KVB_CUDA_OK(cudaFuncSetAttribute(verify_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, vsmem));
+        }
+        if (layer->sinkhorn_iters > 0) {
+            verify_kernel<true><<<dim3(1, layer->kv_heads, P.ksplit), kThreads, vsmem, s>>>(P);
+        } else {
+            verify_kernel<false><<<dim3(1, layer->kv_heads, P.ksplit), kThreads, vsmem, s>>>(P);
+        }
+    } else if (layer->sinkhorn_iters > 0) {
         prefill_kernel<true><<<dim3(P.mtiles, layer->kv_heads, P.ksplit), kThreads, smem, s>>>(P);
     } else {
         prefill_kernel<false><<<dim3(P.mtiles, layer->kv_heads, P.ksplit), kThreads, smem, s>>>(P);
     }
     KVB_CUDA_OK(cudaGetLastError());
     const int total_rows = tokens * layer->q_heads;
-    prefill_merge_kernel<<<total_rows, 256, 0, s>>>(P.ws_m, P.ws_l, P.ws_o, tokens, layer->q_heads, layer->kv_heads, P.mtiles,
-                                                    P.ksplit, layer->dtype, static_cast<uint16_t*>(out), part_m, part_l, part_o);
+    auto merge = P.ksplit <= 16 ? prefill_merge_kernel<2> : P.ksplit <= 32 ? prefill_merge_kernel<4> : P.ksplit <= 64 ? prefill_merge_kernel<8>
+                                                                                                                      : prefill_merge_kernel<16>;
+    merge<<<total_rows, 256, 0, s>>>(P.ws_m, P.ws_l, P.ws_o, tokens, layer->q_heads, layer->kv_heads, P.mtiles, P.ksplit, layer->dtype,
+                                     static_cast<uint16_t*>(out), part_m, part_l, part_o);
     KVB_CUDA_OK(cudaGetLastError());
     return KVB_OK;
 }
