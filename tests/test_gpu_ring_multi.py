@@ -52,7 +52,7 @@ def _worker(rank, world, port, T, ret):
         scale = 1.0 / np.sqrt(D)
 
         def filled(n_tokens, k_rows, v_rows, seed, room):
-            room += 16  # the verify steps below
+            room += 96  # the verify steps and the chunk below
             lp = (n_tokens + room + 63) // 64 + 2
             lp += lp & 1
             L = p.KvarnLayer(D, H, QH, lp, torch.from_numpy(orc.shuffled_table(seed, lp, lp)), device=str(dev))
@@ -115,6 +115,24 @@ def _worker(rank, world, port, T, ret):
             torch.cuda.synchronize()
             ok, msg = attn_close(out_w.float().cpu().numpy(), ref_w.float().cpu().numpy().astype(np.float64), 2.0 ** -8, 5e-3)
             assert ok, f"rank {rank} verify of {w} rows vs the single-GPU verify: {msg}"
+        assert local.errors() == 0 and full.errors() == 0
+        dist.barrier()
+        # ---- a chunk of 64 tokens over the sharded sequence (ShardedChunk: per-rank partials, all-to-all of row shares,
+        #      merge, gather of the finished rows) against the single-GPU chunk attention of the unsharded cache
+        C = 64
+        kc, vc = orc.synth_kv(95, C, H, D, 1), orc.synth_kv(95, C, H, D, 2)
+        qc = torch.from_numpy(orc.synth_q(96, C, QH, D)).to(dev)
+        kcd, vcd = torch.from_numpy(kc).to(dev), torch.from_numpy(vc).to(dev)
+        gpos = torch.arange(base_full, base_full + C, dtype=torch.int32, device=dev)
+        lpos = (torch.arange(base_local, base_local + C, dtype=torch.int32, device=dev) if owner
+                else torch.full((C,), n - 1, dtype=torch.int32, device=dev))
+        chunk = sh.ShardedChunk(local, C)
+        out_c = torch.empty((C, QH, D), dtype=torch.float16, device=dev)
+        chunk.attend(qc, kcd, vcd, lpos, scale, n + steps + 96, out_c)
+        ref_c = full.attn_prefill(qc, kcd, vcd, gpos, scale, T + steps + 96)
+        torch.cuda.synchronize()
+        ok, msg = attn_close(out_c.float().cpu().numpy(), ref_c.float().cpu().numpy().astype(np.float64), 2.0 ** -8, 5e-3)
+        assert ok, f"rank {rank} sharded chunk vs the single-GPU chunk: {msg}"
         assert local.errors() == 0 and full.errors() == 0
         dist.barrier()
         # ---- a peer that never launches: rank 0 calls on a fresh ring with a short wait, rank 1 skips the call
